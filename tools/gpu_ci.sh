@@ -72,12 +72,12 @@ if has ncu; then
       --skip-cpu-baseline > $OUT/ncu_bench.log 2>&1
   echo "ncu launches rc=$?" | tee -a $OUT/summary.txt
   # full capture of the dominant kernel
-  timeout 900 ncu --set full --clock-control none --import-source on \
+  timeout 900 ncu --set full --clock-control none \
       -k regex:paged_attn_persist_kernel -s 4 -c 2 -o $OUT/prof_attn -f \
       python bench.py --steps 1 --warmup 1 --layers 4 --no-graph --skip-cpu-baseline \
       > $OUT/ncu_attn.log 2>&1
   echo "ncu attn rc=$?" | tee -a $OUT/summary.txt
-  timeout 900 ncu --set full --clock-control none --import-source on \
+  timeout 900 ncu --set full --clock-control none \
       -k regex:w4a16_gemm_kernel -s 8 -c 4 -o $OUT/prof_gemm -f \
       python bench.py --steps 1 --warmup 1 --layers 4 --no-graph --skip-cpu-baseline \
       > $OUT/ncu_gemm.log 2>&1
@@ -91,7 +91,7 @@ if has ncul; then
 fi
 
 if has ncuattn; then
-  timeout 600 ncu --set full --clock-control none --import-source on -k regex:paged_attn_mma_kernel \
+  timeout 600 ncu --set full --clock-control none -k regex:paged_attn_mma_kernel \
       -s 6 -c 2 -o $OUT/prof_attn_mma -f python tools/attn_bench.py > $OUT/ncu_attn_mma.log 2>&1
   echo "ncu attn mma rc=$?" | tee -a $OUT/summary.txt
 fi

@@ -17,19 +17,19 @@ timeout 600 ncu --metrics gpu__time_duration.sum --clock-control none -c 600 --c
     --log-file $OUT/launches.csv python bench.py --steps 1 --warmup 1 --layers 4 --no-graph --no-ttft \
     --skip-cpu-baseline > $OUT/ncu_bench.log 2>&1
 echo "ncu launches rc=$?" | tee -a $OUT/summary.txt
-timeout 600 ncu --set full --clock-control none --import-source on \
+timeout 600 ncu --set full --clock-control none \
     -k regex:paged_attn_persist_kernel -s 4 -c 2 -o $OUT/prof_attn -f \
     python bench.py --steps 1 --warmup 1 --layers 4 --no-graph --no-ttft --skip-cpu-baseline > $OUT/ncu_attn.log 2>&1
 echo "ncu attn rc=$?" | tee -a $OUT/summary.txt
-timeout 600 ncu --set full --clock-control none --import-source on \
+timeout 600 ncu --set full --clock-control none \
     -k regex:w4a16_gemm_kernel -s 8 -c 4 -o $OUT/prof_gemm -f \
     python bench.py --steps 1 --warmup 1 --layers 4 --no-graph --no-ttft --skip-cpu-baseline > $OUT/ncu_gemm.log 2>&1
 echo "ncu gemm rc=$?" | tee -a $OUT/summary.txt
-timeout 600 ncu --set full --clock-control none --import-source on \
+timeout 600 ncu --set full --clock-control none \
     -k regex:dense_gemm_kernel -c 1 -o $OUT/prof_dense -f \
     python bench.py --steps 1 --warmup 1 --layers 2 --no-graph --no-ttft --skip-cpu-baseline > $OUT/ncu_dense.log 2>&1
 echo "ncu dense rc=$?" | tee -a $OUT/summary.txt
-timeout 600 ncu --set full --clock-control none --import-source on -k regex:prefill_attn -s 3 -c 1 -f \
+timeout 600 ncu --set full --clock-control none -k regex:prefill_attn -s 3 -c 1 -f \
     -o $OUT/prof_prefill python tools/prefill_trace.py > $OUT/ncu_prefill.log 2>&1
 echo "ncu prefill rc=$?" | tee -a $OUT/summary.txt
 timeout 600 python tools/step_timeline.py --out $OUT/step_timeline.md > $OUT/step_timeline.log 2>&1
