@@ -464,6 +464,81 @@ B200_API int b200_ar_argmax(b200_ar_comm* comm, int64_t* out, const void* logits
                             int64_t n_local, int64_t stride, int dtype, b200_stream_t stream);
 B200_API int b200_ar_destroy(b200_ar_comm* comm);
 
+/* ------------------------------------------------------------------------ *
+ * Sequence mixers and residual arrangements beyond the Llama layer (hyper.cu, latent_attn.cu,
+ * delta_rule.cu, moe.cu).  The reference has no counterpart for these; each entry states its own
+ * arithmetic.  "T" is the activation type named by `dtype`; everything marked fp32 is float on the
+ * device whatever T is.  All strides count elements.  Step metadata as in the attention entry
+ * (q_cu_lens / kv_cu_lens / block_tables of first-slot ids / cu_block_lens), plus
+ *   token_seq   [rows]  index of the step's sequence a packed row belongs to
+ *   state_slots [n_seq] recurrent-state slot of every sequence of the step
+ * A portion whose first row has position 0 starts from zero state instead of reading its slot.
+ * ------------------------------------------------------------------------ */
+/* X[row, s, :] = table[tokens[row], :] for all S residual streams (X fp32 [rows, S, W]). */
+B200_API int b200_embed_streams(float* X, const void* table, const int32_t* tokens, int64_t rows, int64_t W,
+                                int64_t S, int64_t vocab, int dtype, b200_stream_t stream);
+/* u = sum_s collapse[s] X[row, s, :] (collapse NULL: plain sum); out = u * rsqrt(mean(u^2) + eps) *
+ * (offset + weight), written as T and, when out32 is given, also as fp32.  S <= 8. */
+B200_API int b200_hc_norm(void* out, float* out32 /*nullable*/, const float* X, const float* collapse /*nullable*/,
+                          const float* weight, int64_t rows, int64_t W, int64_t S, float eps, float offset,
+                          int dtype, b200_stream_t stream);
+/* out_t = n_t + (n_{t-1} - n_t) * mu; n_{t-1} of a portion's first row comes from state[slot]
+ * (fp32 [n_slots, W]), which then receives the portion's last n. */
+B200_API int b200_token_shift(void* out, const float* n32, const float* mu, float* state, const int32_t* q_cu_lens,
+                              const int32_t* positions, const int32_t* token_seq, const int32_t* state_slots,
+                              int64_t rows, int64_t W, int dtype, b200_stream_t stream);
+/* X[row, t, :] <- sum_s mix[s, t] X[row, s, :] + out_coef[t] * y[row, :] * sigmoid(gate[row, :] + gate_bias)
+ * (gate NULL: no gate; mix NULL: identity; out_coef NULL: ones). */
+B200_API int b200_gated_hc_update(float* X, const void* y, int64_t ldy, const void* gate /*nullable*/, int64_t ldg,
+                                  const float* gate_bias /*nullable*/, const float* mix /*nullable*/,
+                                  const float* out_coef /*nullable*/, int64_t rows, int64_t W, int64_t S,
+                                  int dtype, b200_stream_t stream);
+/* out[rows, n] = act(in[:, :n]) * in[:, n:2n]; act 0 = SiLU, 1 = GELU in its tanh form with tanhf. */
+B200_API int b200_gated_act(void* out, const void* in, int64_t rows, int64_t n, int64_t ld_in, int act, int dtype,
+                            b200_stream_t stream);
+/* out[t, h * d + i] = in[h, t, i] (* sigmoid(gate[t, h * d + i]) when gate is given). */
+B200_API int b200_heads_to_rows(void* out, const void* in, const void* gate /*nullable*/, int64_t ldg, int64_t rows,
+                                int64_t H, int64_t d, int dtype, b200_stream_t stream);
+/* Latent attention, per token: cache[slot] = [rmsnorm(dkv[:rank]) * c_norm_weight | rope(dkv[rank:rank+rd])]
+ * and rope in place on columns [dim, dim + rd) of each of q's H heads of width dim + rd.  The first `dims`
+ * entries of a rotary part rotate as interleaved pairs (2i, 2i+1) by positions * inv_freq[i]; cos and sin are
+ * multiplied by `mult`. */
+B200_API int b200_latent_prepare(void* q, int64_t ldq, const void* dkv, int64_t ld_dkv, void* cache, int64_t ldc,
+                                 const float* c_norm_weight, const float* inv_freq, float mult,
+                                 const int32_t* positions, const int32_t* slots, int64_t rows, int64_t H,
+                                 int64_t dim, int64_t rd, int64_t dims, int64_t rank, float eps, int dtype,
+                                 b200_stream_t stream);
+/* out[h, t, :rank] = sum_j softmax_j((q_absorbed[h, t] . c_j + q_rot[t, h] . kr_j) * scale) c_j over the
+ * cached rows j <= position of t (paged).  q_absorbed: fp32 or T, [H, rows, rank] by strides. */
+B200_API int b200_latent_attn(void* out, int64_t out_head_stride, int64_t out_token_stride, const void* q_absorbed,
+                              int64_t qa_head_stride, int64_t qa_token_stride, int qa_is_fp32, const void* q,
+                              int64_t ldq, const void* cache, int64_t ldc, const int32_t* q_cu_lens,
+                              const int32_t* kv_cu_lens, const int32_t* block_tables, const int32_t* cu_block_lens,
+                              const int32_t* token_seq, int64_t rows, int64_t H, int64_t dim, int64_t rd,
+                              int64_t rank, int64_t block_size, float scale, int dtype, b200_stream_t stream);
+/* Generalised delta rule over each sequence's tokens of the step (see delta_rule.cu); r, k, v, removal and gate
+ * logits are column blocks [H * d] of matrices with row stride ld, the decay logits have row stride ld_decay;
+ * state fp32 [n_slots, H, d, d]. */
+B200_API int b200_delta_rule(void* out, int64_t ldo, const void* r, const void* k, const void* v,
+                             const void* decay_logits, const void* removal_logits, const void* gate_logits,
+                             int64_t ld, int64_t ld_decay, const float* decay_bias, const float* removal_bias,
+                             const float* norm_weight, float* state, const int32_t* q_cu_lens,
+                             const int32_t* positions, const int32_t* state_slots, int64_t n_seq, int64_t H,
+                             int64_t d, float decay_scale, float key_eps, float eps, int dtype,
+                             b200_stream_t stream);
+/* Mixture of experts (see moe.cu). */
+B200_API int b200_moe_route(int32_t* expert_ids, float* weights, const void* h, int64_t ldh,
+                            const float* router_weight, int64_t rows, int64_t W, int64_t E, int64_t top, int dtype,
+                            b200_stream_t stream);
+B200_API int b200_moe_plan(int32_t* offsets, int32_t* sorted_pair, int32_t* pos_of_pair, const int32_t* expert_ids,
+                           int64_t n_pairs, int64_t E, b200_stream_t stream);
+B200_API int b200_grouped_gemm(void* C, int64_t ldc, const void* A, int64_t lda, const int32_t* sorted_pair /*nullable*/,
+                               const float* pair_scale /*nullable*/, int64_t top, const void* weights,
+                               const int32_t* offsets, int64_t n_rows, int64_t E, int64_t N, int64_t K, int dtype,
+                               b200_stream_t stream);
+B200_API int b200_moe_combine(void* out, const void* Y, int64_t ldy, const int32_t* pos_of_pair, int64_t rows,
+                              int64_t W, int64_t top, int dtype, b200_stream_t stream);
+
 #ifdef __cplusplus
 } /* extern "C" */
 #endif

@@ -94,28 +94,110 @@ SIGNATURES = {
     "b200_ar_allreduce_splitk_norm": (_int, [_vp, _vp, _vp, _vp, _int, _i64, _vp, _i64, _i64, _f32, _int, _vp]),
     "b200_ar_argmax": (_int, [_vp, _vp, _vp, _i64, _i64, _i64, _int, _vp]),
     "b200_ar_destroy": (_int, [_vp]),
+    # residual streams, latent attention, delta rule, mixture of experts (hyper.cu, latent_attn.cu,
+    # delta_rule.cu, moe.cu)
+    "b200_embed_streams": (_int, [_vp, _vp, _vp, _i64, _i64, _i64, _i64, _int, _vp]),
+    "b200_hc_norm": (_int, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _f32, _f32, _int, _vp]),
+    "b200_token_shift": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _int, _vp]),
+    "b200_gated_hc_update": (_int, [_vp, _vp, _i64, _vp, _i64, _vp, _vp, _vp, _i64, _i64, _i64, _int, _vp]),
+    "b200_gated_act": (_int, [_vp, _vp, _i64, _i64, _i64, _int, _int, _vp]),
+    "b200_heads_to_rows": (_int, [_vp, _vp, _vp, _i64, _i64, _i64, _i64, _int, _vp]),
+    "b200_latent_prepare": (_int, [_vp, _i64, _vp, _i64, _vp, _i64, _vp, _vp, _f32, _vp, _vp, _i64, _i64,
+                                   _i64, _i64, _i64, _i64, _f32, _int, _vp]),
+    "b200_latent_attn": (_int, [_vp, _i64, _i64, _vp, _i64, _i64, _int, _vp, _i64, _vp, _i64, _vp, _vp, _vp,
+                                _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i64, _f32, _int, _vp]),
+    "b200_delta_rule": (_int, [_vp, _i64, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _vp, _vp, _vp, _vp, _vp,
+                               _vp, _vp, _i64, _i64, _i64, _f32, _f32, _f32, _int, _vp]),
+    "b200_moe_route": (_int, [_vp, _vp, _vp, _i64, _vp, _i64, _i64, _i64, _i64, _int, _vp]),
+    "b200_moe_plan": (_int, [_vp, _vp, _vp, _vp, _i64, _i64, _vp]),
+    "b200_grouped_gemm": (_int, [_vp, _i64, _vp, _i64, _vp, _vp, _i64, _vp, _vp, _i64, _i64, _i64, _i64,
+                                 _int, _vp]),
+    "b200_moe_combine": (_int, [_vp, _vp, _i64, _vp, _i64, _i64, _i64, _int, _vp]),
 }
 
+# Which source files a partial library needs for a group of entry points.  The whole library
+# (libb200decode.so, every source) serves everything; where it has not been built, `ensure()` compiles
+# just the sources a model asks for into a library of its own.
+ALL_SOURCES = ("runtime.cu", "elementwise.cu", "sampling.cu", "paged_attn.cu", "prefill_attn.cu", "w4a16.cu",
+               "dense.cu", "allreduce.cu", "hyper.cu", "latent_attn.cu", "delta_rule.cu", "moe.cu")
+
 _lib: Optional[C.CDLL] = None
+_lib_sources: frozenset = frozenset()
+
+
+def _bind(lib: C.CDLL, partial: bool) -> C.CDLL:
+    for name, (res, args) in SIGNATURES.items():
+        try:
+            fn = getattr(lib, name)
+        except AttributeError:
+            if partial:     # a partial library exports the entry points of its sources only
+                continue
+            raise
+        fn.restype = res
+        fn.argtypes = args
+    return lib
+
+
+def has(name: str) -> bool:
+    """Whether the loaded library exports an entry point (a partial library may not)."""
+    try:
+        getattr(load(), name)
+        return True
+    except AttributeError:
+        return False
 
 
 def load() -> C.CDLL:
     """Load (once) and return the shared library; raises if it was not built."""
-    global _lib
+    global _lib, _lib_sources
     if _lib is not None:
         return _lib
     if not os.path.exists(LIB_PATH):
         raise RuntimeError(
             f"{LIB_PATH} not found: the CUDA extension is not built. Build it with "
-            "`python -c \"import __graft_entry__ as g; g.build()\"` (needs nvcc). "
-            "There is no CPU / PyTorch fallback.")
-    lib = C.CDLL(LIB_PATH)
-    for name, (res, args) in SIGNATURES.items():
-        fn = getattr(lib, name)  # AttributeError if the symbol is not exported
-        fn.restype = res
-        fn.argtypes = args
-    _lib = lib
-    return lib
+            "`python -c \"import __graft_entry__ as g; g.build()\"` (needs nvcc), or let a model "
+            "build the part it needs (scalellm_b200._lib.ensure). There is no CPU / PyTorch fallback.")
+    _lib = _bind(C.CDLL(LIB_PATH), False)
+    _lib_sources = frozenset(ALL_SOURCES)
+    return _lib
+
+
+def ensure(sources) -> C.CDLL:
+    """Make sure a library with (at least) these csrc sources is loaded.  The whole library is used
+    when it exists; otherwise the named sources (plus runtime.cu) are compiled with nvcc for sm_100a
+    into scalellm_b200/libb200part-<key>.so — nothing else is built — and that library is loaded."""
+    global _lib, _lib_sources
+    need = frozenset(sources) | {"runtime.cu"}
+    unknown = need - set(ALL_SOURCES)
+    if unknown:
+        raise ValueError(f"unknown csrc sources {sorted(unknown)}")
+    if _lib is not None and need <= _lib_sources:
+        return _lib
+    if os.path.exists(LIB_PATH) and _lib is None:
+        return load()
+    need = need | _lib_sources
+    srcs = [s for s in ALL_SOURCES if s in need]
+    import hashlib
+    key = hashlib.sha1(" ".join(srcs).encode()).hexdigest()[:10]
+    out = os.path.join(_HERE, f"libb200part-{key}.so")
+    csrc = os.path.join(_HERE, "csrc")
+    deps = [os.path.join(csrc, s) for s in srcs] + [os.path.join(csrc, "common.cuh"),
+                                                    os.path.join(_HERE, "..", "include", "b200_decode.h")]
+    import fcntl
+    import subprocess
+    os.makedirs(os.path.join(csrc, "build"), exist_ok=True)
+    with open(os.path.join(csrc, "build", ".lock"), "w") as lock:
+        fcntl.flock(lock, fcntl.LOCK_EX)
+        if not (os.path.exists(out) and all(os.path.getmtime(out) >= os.path.getmtime(d) for d in deps)):
+            jobs = str(max(1, min(8, os.cpu_count() or 1)))
+            r = subprocess.run(["make", "-C", csrc, "-j", jobs, "SRCS=" + " ".join(srcs),
+                                "OUT=../" + os.path.basename(out)], capture_output=True, text=True)
+            if r.returncode != 0:
+                raise RuntimeError("nvcc build of " + os.path.basename(out) + " failed:\n" + r.stdout[-3000:]
+                                   + "\n" + r.stderr[-3000:])
+    _lib = _bind(C.CDLL(out), True)
+    _lib_sources = frozenset(srcs)
+    return _lib
 
 
 def check(rc: int) -> None:

@@ -1,0 +1,245 @@
+// moe.cu — token-choice mixture of experts: router, expert plan, grouped GEMM, combine.
+//
+//   route    z = Wr h in fp32 (Wr kept in fp32), s = sigmoid(z); the `top` largest per token are
+//            chosen (first index wins a tie); the routing weight of a choice is s itself.
+//   plan     counting sort of the (token, choice) pairs by expert: offsets[E + 1], the pair at each
+//            sorted position and the sorted position of each pair — all on the device, so a step
+//            never synchronises with the host.
+//   grouped  C[pos, :] = A(pos) W_e^T for every sorted position of expert e.  A(pos) is either row
+//            pos of a sorted activation matrix, or (gather form) the routing weight times the
+//            token's input row: the weight scales what the expert reads, not what it returns.
+//            64 x 64 tiles, fp32 accumulation in k order: a row's result does not depend on where
+//            the row sits in a tile or on what shares the tile.
+//   combine  out[t] = sum over choices of Y[position of (t, choice)], summed in choice order.
+#include "common.cuh"
+
+namespace b200 {
+namespace {
+
+constexpr int kMaxExperts = 1024;
+constexpr int kMaxTop = 32;
+constexpr int BM = 64, BN = 64, BK = 16;
+
+template <typename T>
+__global__ void __launch_bounds__(128)
+moe_route_kernel(int* __restrict__ ids, float* __restrict__ weights, const T* __restrict__ h, int64_t ldh,
+                 const float* __restrict__ Wr, int W, int E, int top) {
+  __shared__ float z_s[kMaxExperts];
+  const int row = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const T* x = h + (size_t)row * ldh;
+  for (int e = warp; e < E; e += 4) {
+    const float* w = Wr + (size_t)e * W;
+    float acc = 0.0f;
+    for (int i = lane; i < W; i += 32) acc += Num<T>::to_f(x[i]) * w[i];
+    acc = warp_sum(acc);
+    if (lane == 0) z_s[e] = acc;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int k = 0; k < top; ++k) {
+      int best = 0;
+      float bz = -INFINITY;
+      for (int e = 0; e < E; ++e) {
+        const float z = z_s[e];
+        if (z > bz) { bz = z; best = e; }
+      }
+      ids[(size_t)row * top + k] = best;
+      weights[(size_t)row * top + k] = 1.0f / (1.0f + expf(-bz));
+      z_s[best] = -INFINITY;
+    }
+  }
+}
+
+__global__ void __launch_bounds__(1024)
+moe_plan_kernel(int* __restrict__ offsets, int* __restrict__ sorted_pair, int* __restrict__ pos_of_pair,
+                const int* __restrict__ ids, int n_pairs, int E) {
+  __shared__ int cnt[kMaxExperts + 1];
+  for (int e = threadIdx.x; e <= E; e += blockDim.x) cnt[e] = 0;
+  __syncthreads();
+  for (int p = threadIdx.x; p < n_pairs; p += blockDim.x) atomicAdd(&cnt[ids[p]], 1);
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int run = 0;
+    for (int e = 0; e < E; ++e) {
+      const int c = cnt[e];
+      offsets[e] = run;
+      cnt[e] = run;
+      run += c;
+    }
+    offsets[E] = run;
+  }
+  __syncthreads();
+  for (int p = threadIdx.x; p < n_pairs; p += blockDim.x) {
+    const int pos = atomicAdd(&cnt[ids[p]], 1);
+    sorted_pair[pos] = p;
+    pos_of_pair[p] = pos;
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+grouped_gemm_kernel(T* __restrict__ C, int64_t ldc, const T* __restrict__ A, int64_t lda,
+                    const int* __restrict__ sorted_pair, const float* __restrict__ pair_scale, int top,
+                    const T* __restrict__ Wst, const int* __restrict__ offsets, int E, int N, int K) {
+  __shared__ float As[BK][BM + 4], Bs[BK][BN + 4];
+  __shared__ int src_row[BM];
+  __shared__ float src_scale[BM];
+  // which expert and which of its row tiles is this CTA's
+  int e = 0, tile = blockIdx.y, lo = 0, hi = 0;
+  for (; e < E; ++e) {
+    lo = offsets[e];
+    hi = offsets[e + 1];
+    const int nt = (hi - lo + BM - 1) / BM;
+    if (tile < nt) break;
+    tile -= nt;
+  }
+  if (e == E) return;
+  const int m0 = lo + tile * BM, n0 = blockIdx.x * BN;
+  const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
+  if (tid < BM) {
+    const int pos = m0 + tid;
+    int src = -1;
+    float sc = 1.0f;
+    if (pos < hi) {
+      if (sorted_pair) {
+        const int p = sorted_pair[pos];
+        src = p / top;
+        sc = pair_scale ? pair_scale[p] : 1.0f;
+      } else {
+        src = pos;
+      }
+    }
+    src_row[tid] = src;
+    src_scale[tid] = sc;
+  }
+  __syncthreads();
+  const T* Wm = Wst + (size_t)e * N * K;
+  float acc[4][4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) acc[i][j] = 0.0f;
+  for (int k0 = 0; k0 < K; k0 += BK) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int idx = tid + 256 * i;
+      const int m = idx >> 4, kk = idx & 15;
+      const int src = src_row[m];
+      float a = 0.0f, b = 0.0f;
+      if (k0 + kk < K) {
+        if (src >= 0) a = Num<T>::to_f(A[(size_t)src * lda + k0 + kk]) * src_scale[m];
+        if (n0 + m < N) b = Num<T>::to_f(Wm[(size_t)(n0 + m) * K + k0 + kk]);
+      }
+      As[kk][m] = a;
+      Bs[kk][m] = b;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int kk = 0; kk < BK; ++kk) {
+      float a[4], b[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) a[i] = As[kk][ty * 4 + i];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) b[j] = Bs[kk][tx * 4 + j];
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] += a[i] * b[j];
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int pos = m0 + ty * 4 + i;
+    if (pos >= hi) continue;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int n = n0 + tx * 4 + j;
+      if (n < N) C[(size_t)pos * ldc + n] = Num<T>::from_f(acc[i][j]);
+    }
+  }
+}
+
+template <typename T>
+__global__ void moe_combine_kernel(T* __restrict__ out, const T* __restrict__ Y, int64_t ldy,
+                                   const int* __restrict__ pos_of_pair, int W, int top) {
+  const int row = blockIdx.x;
+  for (int i = threadIdx.x; i < W; i += blockDim.x) {
+    float acc = 0.0f;
+    for (int k = 0; k < top; ++k)
+      acc += Num<T>::to_f(Y[(size_t)pos_of_pair[(size_t)row * top + k] * ldy + i]);
+    out[(size_t)row * W + i] = Num<T>::from_f(acc);
+  }
+}
+
+#define MOE_DISPATCH(dtype, ...)                                                 \
+  switch (dtype) {                                                               \
+    case B200_BF16: { using T = __nv_bfloat16; __VA_ARGS__; break; }             \
+    case B200_FP16: { using T = __half; __VA_ARGS__; break; }                    \
+    case B200_FP32: { using T = float; __VA_ARGS__; break; }                     \
+    default: return set_error(B200_ERR_INVALID_ARG, "bad dtype %d", dtype);      \
+  }
+
+}  // namespace
+}  // namespace b200
+
+using namespace b200;
+
+extern "C" {
+
+int b200_moe_route(int32_t* expert_ids, float* weights, const void* h, int64_t ldh,
+                   const float* router_weight, int64_t rows, int64_t W, int64_t E, int64_t top, int dtype,
+                   b200_stream_t stream) {
+  if (rows == 0) return B200_OK;
+  B200_CHECK_ARG(expert_ids && weights && h && router_weight, "moe_route: null pointer");
+  B200_CHECK_ARG(rows > 0 && W > 0 && ldh >= W && E >= 1 && E <= kMaxExperts && top >= 1 && top <= E &&
+                     top <= kMaxTop,
+                 "moe_route: bad shape (experts <= 1024, top <= min(experts, 32))");
+  auto st = static_cast<cudaStream_t>(stream);
+  MOE_DISPATCH(dtype, (moe_route_kernel<T><<<(unsigned)rows, 128, 0, st>>>(
+                          expert_ids, weights, static_cast<const T*>(h), ldh, router_weight, (int)W, (int)E,
+                          (int)top)));
+  B200_LAUNCH_OK("moe_route_kernel");
+  return B200_OK;
+}
+
+int b200_moe_plan(int32_t* offsets, int32_t* sorted_pair, int32_t* pos_of_pair, const int32_t* expert_ids,
+                  int64_t n_pairs, int64_t E, b200_stream_t stream) {
+  B200_CHECK_ARG(offsets && sorted_pair && pos_of_pair && expert_ids, "moe_plan: null pointer");
+  B200_CHECK_ARG(n_pairs >= 0 && n_pairs < (1ll << 31) && E >= 1 && E <= kMaxExperts, "moe_plan: bad shape");
+  moe_plan_kernel<<<1, 1024, 0, static_cast<cudaStream_t>(stream)>>>(offsets, sorted_pair, pos_of_pair,
+                                                                    expert_ids, (int)n_pairs, (int)E);
+  B200_LAUNCH_OK("moe_plan_kernel");
+  return B200_OK;
+}
+
+int b200_grouped_gemm(void* C, int64_t ldc, const void* A, int64_t lda, const int32_t* sorted_pair,
+                      const float* pair_scale, int64_t top, const void* weights, const int32_t* offsets,
+                      int64_t n_rows, int64_t E, int64_t N, int64_t K, int dtype, b200_stream_t stream) {
+  if (n_rows == 0) return B200_OK;
+  B200_CHECK_ARG(C && A && weights && offsets, "grouped_gemm: null pointer");
+  B200_CHECK_ARG(n_rows > 0 && E >= 1 && N > 0 && K > 0 && ldc >= N && lda >= K && top >= 1 &&
+                     (n_rows + BM - 1) / BM + E <= 65535,
+                 "grouped_gemm: bad shape");
+  dim3 grid((unsigned)((N + BN - 1) / BN), (unsigned)((n_rows + BM - 1) / BM + E));
+  auto st = static_cast<cudaStream_t>(stream);
+  MOE_DISPATCH(dtype, (grouped_gemm_kernel<T><<<grid, 256, 0, st>>>(
+                          static_cast<T*>(C), ldc, static_cast<const T*>(A), lda, sorted_pair, pair_scale,
+                          (int)top, static_cast<const T*>(weights), offsets, (int)E, (int)N, (int)K)));
+  B200_LAUNCH_OK("grouped_gemm_kernel");
+  return B200_OK;
+}
+
+int b200_moe_combine(void* out, const void* Y, int64_t ldy, const int32_t* pos_of_pair, int64_t rows,
+                     int64_t W, int64_t top, int dtype, b200_stream_t stream) {
+  if (rows == 0) return B200_OK;
+  B200_CHECK_ARG(out && Y && pos_of_pair, "moe_combine: null pointer");
+  B200_CHECK_ARG(rows > 0 && W > 0 && ldy >= W && top >= 1, "moe_combine: bad shape");
+  auto st = static_cast<cudaStream_t>(stream);
+  MOE_DISPATCH(dtype, (moe_combine_kernel<T><<<(unsigned)rows, 128, 0, st>>>(
+                          static_cast<T*>(out), static_cast<const T*>(Y), ldy, pos_of_pair, (int)W, (int)top)));
+  B200_LAUNCH_OK("moe_combine_kernel");
+  return B200_OK;
+}
+
+}  // extern "C"

@@ -271,6 +271,8 @@ class HostBatch:
     cu_block_lens: np.ndarray   # int32 [B+1]
     q_max: int
     kv_max: int
+    token_seq: Optional[np.ndarray] = None     # int32 [T]  sequence index (within the step) of every row
+    state_slots: Optional[np.ndarray] = None   # int32 [B]  recurrent-state slot of every sequence
 
 
 class BlockPool:
@@ -301,6 +303,88 @@ class BlockPool:
 
     def n_blocks_of(self, seq: int) -> int:
         return len(self.seq_blocks[seq])
+
+    # -- sequences that come and go (the serving engine): blocks are taken as a sequence grows and go
+    # back to the free list when it ends; a freed sequence index is handed out again.
+    def open_sequence(self) -> int:
+        for i, b in enumerate(self.seq_blocks):
+            if b is None:
+                self.seq_blocks[i] = []
+                return i
+        return self.add_sequence(0)
+
+    def reserve(self, seq: int, n_tokens: int) -> None:
+        """Give `seq` blocks for n_tokens tokens in all (no-op if it has them)."""
+        blocks = self.seq_blocks[seq]
+        nb = (n_tokens + self.block_size - 1) // self.block_size
+        extra = nb - len(blocks)
+        if extra <= 0:
+            return
+        if extra > len(self.free):
+            raise RuntimeError("block pool exhausted")
+        if nb > self._table.shape[1]:
+            t = np.zeros((self._table.shape[0], nb), dtype=np.int32)
+            t[:, : self._table.shape[1]] = self._table
+            self._table = t
+        for _ in range(extra):
+            b = self.free.pop()
+            self._table[seq, len(blocks)] = b * self.block_size
+            blocks.append(b)
+
+    def release(self, seq: int) -> None:
+        self.free.extend(self.seq_blocks[seq])
+        self.seq_blocks[seq] = None
+        self._table[seq, :] = 0
+
+    def n_free_blocks(self) -> int:
+        return len(self.free)
+
+
+class StateSlotPool:
+    """Slots of per-sequence recurrent state (token shift rows, delta-rule matrices).  A slot is not
+    cleared when it is handed out again: a sequence's first portion starts at position 0, which the
+    kernels take as "start from zero state"."""
+
+    def __init__(self, n_slots: int):
+        self.free = list(range(n_slots - 1, -1, -1))
+
+    def take(self) -> int:
+        if not self.free:
+            raise RuntimeError("no free state slot")
+        return self.free.pop()
+
+    def give_back(self, slot: int) -> None:
+        self.free.append(slot)
+
+
+def build_step_batch(pool: BlockPool, seqs: List[int], new_tokens: List[List[int]], cached: List[int],
+                     state_slots: Optional[List[int]] = None) -> HostBatch:
+    """One step's InputParameters on the host for given token ids: sequence seqs[i] of the pool has
+    cached[i] tokens in the cache and runs new_tokens[i] now (a prompt portion or one decoded token).
+    The pool must already hold blocks for cached[i] + len(new_tokens[i]) tokens (BlockPool.reserve)."""
+    bs = pool.block_size
+    B = len(seqs)
+    ql = np.asarray([len(t) for t in new_tokens], dtype=np.int64)
+    kv = np.asarray(cached, dtype=np.int64) + ql
+    nb = (kv + bs - 1) // bs
+    q_cu = np.zeros(B + 1, dtype=np.int64)
+    np.cumsum(ql, out=q_cu[1:])
+    kv_cu = np.zeros(B + 1, dtype=np.int64)
+    np.cumsum(kv, out=kv_cu[1:])
+    blk_cu = np.zeros(B + 1, dtype=np.int64)
+    np.cumsum(nb, out=blk_cu[1:])
+    T = int(q_cu[-1])
+    seq_of_tok = np.repeat(np.arange(B), ql)
+    positions = np.arange(T) - q_cu[seq_of_tok] + (kv - ql)[seq_of_tok]
+    table = pool._table[np.asarray(seqs, dtype=np.int64)] if B else np.zeros((0, 0), dtype=np.int32)
+    assert all(len(pool.seq_blocks[s]) >= n for s, n in zip(seqs, nb)), "sequence outgrew its blocks"
+    slots = table[seq_of_tok, positions // bs].astype(np.int64) + positions % bs if T else np.zeros(0)
+    tables = table[np.arange(table.shape[1])[None, :] < nb[:, None]] if B else np.zeros(0)
+    tokens = np.concatenate([np.asarray(t, dtype=np.int64) for t in new_tokens]) if B else np.zeros(0)
+    i32 = lambda x: np.ascontiguousarray(x, dtype=np.int32)
+    return HostBatch(i32(tokens), i32(positions), i32(q_cu), i32(kv_cu), i32(slots), i32(tables), i32(blk_cu),
+                     int(ql.max()) if B else 0, int(kv.max()) if B else 0, i32(seq_of_tok),
+                     None if state_slots is None else i32(state_slots))
 
 
 def build_decode_batch(pool: BlockPool, kv_lens: List[int], q_lens: List[int], vocab: int,
@@ -338,12 +422,12 @@ class StepBuffers:
     H2D copies): the seven int32 arrays live at fixed offsets, so a step is ONE host->device copy
     and the device views keep their addresses (CUDA-graph safe)."""
 
-    FIELDS = ("tokens", "positions", "slots", "q_cu", "kv_cu", "blk_cu", "tables")
+    FIELDS = ("tokens", "positions", "slots", "q_cu", "kv_cu", "blk_cu", "token_seq", "state_slots", "tables")
 
     def __init__(self, device, max_tokens: int, max_seqs: int, max_blocks: int):
         caps = {"tokens": max_tokens, "positions": max_tokens, "slots": max_tokens,
                 "q_cu": max_seqs + 1, "kv_cu": max_seqs + 1, "blk_cu": max_seqs + 1,
-                "tables": max_blocks}
+                "token_seq": max_tokens, "state_slots": max_seqs, "tables": max_blocks}
         self.device = device
         self.off, total = {}, 0
         for f in self.FIELDS:
@@ -362,6 +446,8 @@ class StepBuffers:
         """Async H2D of one step's metadata from pinned memory on the current stream."""
         arrs = {"tokens": hb.tokens, "positions": hb.positions, "slots": hb.new_cache_slots,
                 "q_cu": hb.q_cu_lens, "kv_cu": hb.kv_cu_lens, "blk_cu": hb.cu_block_lens,
+                "token_seq": hb.token_seq if hb.token_seq is not None else hb.tokens[:0],
+                "state_slots": hb.state_slots if hb.state_slots is not None else hb.tokens[:0],
                 "tables": hb.block_tables}
         view = {}
         for f in self.FIELDS:
@@ -376,7 +462,9 @@ class StepBuffers:
         params = InputParameters(
             num_sequences=B, q_cu_seq_lens=view["q_cu"], kv_cu_seq_lens=view["kv_cu"],
             kv_max_seq_len=hb.kv_max, q_max_seq_len=hb.q_max, new_cache_slots=view["slots"],
-            block_tables=view["tables"], cu_block_lens=view["blk_cu"])
+            block_tables=view["tables"], cu_block_lens=view["blk_cu"],
+            token_seq=view["token_seq"] if hb.token_seq is not None else None,
+            state_slots=view["state_slots"] if hb.state_slots is not None else None)
         return view["tokens"], view["positions"], params
 
 

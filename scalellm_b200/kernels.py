@@ -192,7 +192,8 @@ def silu_with_mul(input: torch.Tensor) -> torch.Tensor:
 def dense_supported(x: torch.Tensor, weight: torch.Tensor) -> bool:
     """Shapes / dtypes the tcgen05 dense kernel takes (rank-invariant: sizes, dtypes and strides of
     freshly allocated activations only)."""
-    return (x.is_cuda and x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16
+    return (x.is_cuda and _lib.has("b200_dense_gemm")
+            and x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16
             and x.dim() >= 2 and x.shape[-1] % 64 == 0 and weight.shape[0] % 8 == 0
             and weight.stride(1) == 1 and weight.stride(0) % 8 == 0)
 
@@ -619,3 +620,218 @@ def launch_count() -> int:
 
 def launch_count_reset() -> None:
     _lib.load().b200_launch_count_reset()
+
+
+# ---------------------------------------------------------------------------
+# residual streams (hyper-connections), offset RMS norm, token shift, gated sublayer results
+# (csrc/hyper.cu).  Streams, norm weights, shift vectors, biases and coefficients are fp32.
+# ---------------------------------------------------------------------------
+def _f32(*ts: Optional[torch.Tensor]) -> None:
+    for t in ts:
+        if t is not None and (t.dtype != torch.float32 or not t.is_contiguous()):
+            raise TypeError("expected a contiguous float32 tensor")
+
+
+def embed_streams(table: torch.Tensor, tokens: torch.Tensor, n_streams: int) -> torch.Tensor:
+    """X [rows, S, W] fp32 with every stream equal to the token's embedding row."""
+    _cuda(table, tokens)
+    _check_i32(tokens)
+    assert table.dim() == 2 and table.is_contiguous()
+    X = torch.empty((tokens.numel(), n_streams, table.shape[1]), dtype=torch.float32, device=table.device)
+    check(_lib.load().b200_embed_streams(_p(X), _p(table), _p(tokens), tokens.numel(), table.shape[1],
+                                         n_streams, table.shape[0], _dt(table), _stream()))
+    return X
+
+
+def hc_norm(X: torch.Tensor, collapse: Optional[torch.Tensor], weight: torch.Tensor, eps: float,
+            offset: float, dtype: torch.dtype, want_fp32: bool = False):
+    """Collapse the streams (sum_s collapse[s] X[:, s]) and RMS-normalise with weight (offset + w).
+    Returns the rows as `dtype` and, if asked, also in fp32 (for the token shift)."""
+    _cuda(X, weight)
+    _f32(X, collapse, weight)
+    rows, S, W = X.shape
+    out = torch.empty((rows, W), dtype=dtype, device=X.device)
+    out32 = torch.empty((rows, W), dtype=torch.float32, device=X.device) if want_fp32 else None
+    check(_lib.load().b200_hc_norm(_p(out), _p(out32), _p(X), _p(collapse), _p(weight), rows, W, S, eps,
+                                   offset, _DT[dtype], _stream()))
+    return (out, out32) if want_fp32 else out
+
+
+def token_shift(n32: torch.Tensor, mu: torch.Tensor, state: torch.Tensor, q_cu: torch.Tensor,
+                positions: torch.Tensor, token_seq: torch.Tensor, state_slots: torch.Tensor,
+                dtype: torch.dtype) -> torch.Tensor:
+    _cuda(n32, mu, state)
+    _f32(n32, mu, state)
+    _check_i32(q_cu, positions, token_seq, state_slots)
+    rows, W = n32.shape
+    assert state.dim() == 2 and state.shape[1] == W
+    out = torch.empty((rows, W), dtype=dtype, device=n32.device)
+    check(_lib.load().b200_token_shift(_p(out), _p(n32), _p(mu), _p(state), _p(q_cu), _p(positions),
+                                       _p(token_seq), _p(state_slots), rows, W, _DT[dtype], _stream()))
+    return out
+
+
+def gated_hc_update(X: torch.Tensor, y: torch.Tensor, gate: Optional[torch.Tensor],
+                    gate_bias: Optional[torch.Tensor], mix: Optional[torch.Tensor],
+                    out_coef: Optional[torch.Tensor]) -> None:
+    """In place: X[:, t] <- sum_s mix[s, t] X[:, s] + out_coef[t] * y * sigmoid(gate + gate_bias)."""
+    _cuda(X, y, gate)
+    _f32(X, gate_bias, mix, out_coef)
+    rows, S, W = X.shape
+    assert y.shape == (rows, W) and y.stride(1) == 1
+    assert gate is None or (gate.shape == (rows, W) and gate.stride(1) == 1 and gate.dtype == y.dtype)
+    check(_lib.load().b200_gated_hc_update(_p(X), _p(y), y.stride(0), _p(gate),
+                                           gate.stride(0) if gate is not None else 0, _p(gate_bias),
+                                           _p(mix), _p(out_coef), rows, W, S, _dt(y), _stream()))
+
+
+def gated_act(gate_up: torch.Tensor, act: str) -> torch.Tensor:
+    """act(gate) * up for a [rows, 2n] matrix [gate | up]; act: "silu" or "gelu_tanh" (tanhf)."""
+    _cuda(gate_up)
+    assert gate_up.dim() == 2 and gate_up.stride(1) == 1 and gate_up.shape[1] % 2 == 0
+    n = gate_up.shape[1] // 2
+    out = torch.empty((gate_up.shape[0], n), dtype=gate_up.dtype, device=gate_up.device)
+    check(_lib.load().b200_gated_act(_p(out), _p(gate_up), gate_up.shape[0], n, gate_up.stride(0),
+                                     {"silu": 0, "gelu_tanh": 1}[act], _dt(gate_up), _stream()))
+    return out
+
+
+def heads_to_rows(x: torch.Tensor, gate: Optional[torch.Tensor]) -> torch.Tensor:
+    """[H, rows, d] -> [rows, H * d], optionally times sigmoid(gate [rows, H * d])."""
+    _cuda(x, gate)
+    assert x.dim() == 3 and x.is_contiguous()
+    H, rows, d = x.shape
+    assert gate is None or (gate.shape == (rows, H * d) and gate.stride(1) == 1 and gate.dtype == x.dtype)
+    out = torch.empty((rows, H * d), dtype=x.dtype, device=x.device)
+    check(_lib.load().b200_heads_to_rows(_p(out), _p(x), _p(gate), gate.stride(0) if gate is not None else 0,
+                                         rows, H, d, _dt(x), _stream()))
+    return out
+
+
+# ---------------------------------------------------------------------------
+# latent attention (csrc/latent_attn.cu)
+# ---------------------------------------------------------------------------
+def latent_prepare(q: torch.Tensor, dkv: torch.Tensor, cache: torch.Tensor, c_norm_weight: torch.Tensor,
+                   inv_freq: torch.Tensor, mult: float, positions: torch.Tensor, slots: torch.Tensor,
+                   n_heads: int, dim: int, rot_dim: int, rot_dims: int, rank: int, eps: float) -> None:
+    """In place on q (rotary part of every head) and on the cache rows `slots` (latent + rotary key)."""
+    _cuda(q, dkv, cache)
+    _f32(c_norm_weight, inv_freq)
+    _check_i32(positions, slots)
+    assert q.dim() == 2 and q.stride(1) == 1 and dkv.dim() == 2 and dkv.stride(1) == 1
+    assert cache.dim() == 2 and cache.stride(1) == 1 and cache.shape[1] == rank + rot_dim
+    assert q.dtype == dkv.dtype == cache.dtype and inv_freq.numel() == rot_dims // 2
+    check(_lib.load().b200_latent_prepare(_p(q), q.stride(0), _p(dkv), dkv.stride(0), _p(cache), cache.stride(0),
+                                          _p(c_norm_weight), _p(inv_freq), mult, _p(positions), _p(slots),
+                                          q.shape[0], n_heads, dim, rot_dim, rot_dims, rank, eps, _dt(q),
+                                          _stream()))
+
+
+def latent_attn(q_absorbed: torch.Tensor, q: torch.Tensor, cache: torch.Tensor, q_cu: torch.Tensor,
+                kv_cu: torch.Tensor, block_tables: torch.Tensor, cu_block_lens: torch.Tensor,
+                token_seq: torch.Tensor, n_heads: int, dim: int, rot_dim: int, rank: int, block_size: int,
+                scale: float) -> torch.Tensor:
+    """q_absorbed [H, rows, rank] (fp32 or q's dtype), q [rows, >= H * (dim + rot_dim)] with the rotary
+    parts already rotated; returns the attention-weighted latents [H, rows, rank] in q's dtype."""
+    _cuda(q_absorbed, q, cache)
+    _check_i32(q_cu, kv_cu, block_tables, cu_block_lens, token_seq)
+    rows = q.shape[0]
+    assert q_absorbed.shape == (n_heads, rows, rank) and q_absorbed.stride(2) == 1
+    assert q_absorbed.dtype in (torch.float32, q.dtype) and q.stride(1) == 1 and cache.dtype == q.dtype
+    out = torch.empty((n_heads, rows, rank), dtype=q.dtype, device=q.device)
+    check(_lib.load().b200_latent_attn(_p(out), out.stride(0), out.stride(1), _p(q_absorbed),
+                                       q_absorbed.stride(0), q_absorbed.stride(1),
+                                       1 if q_absorbed.dtype == torch.float32 else 0, _p(q), q.stride(0),
+                                       _p(cache), cache.stride(0), _p(q_cu), _p(kv_cu), _p(block_tables),
+                                       _p(cu_block_lens), _p(token_seq), rows, n_heads, dim, rot_dim, rank,
+                                       block_size, scale, _dt(q), _stream()))
+    return out
+
+
+# ---------------------------------------------------------------------------
+# generalised delta rule (csrc/delta_rule.cu)
+# ---------------------------------------------------------------------------
+def delta_rule(r: torch.Tensor, k: torch.Tensor, v: torch.Tensor, decay_logits: torch.Tensor,
+               removal_logits: torch.Tensor, gate_logits: torch.Tensor, decay_bias: torch.Tensor,
+               removal_bias: torch.Tensor, norm_weight: torch.Tensor, state: torch.Tensor,
+               q_cu: torch.Tensor, positions: torch.Tensor, state_slots: torch.Tensor, n_heads: int,
+               head_dim: int, decay_scale: float, key_eps: float, eps: float) -> torch.Tensor:
+    """r, k, v, removal and gate logits: column blocks [rows, H * d] of one matrix (same row stride);
+    state fp32 [n_slots, H, d, d], updated in place.  Returns [rows, H * d]."""
+    _cuda(r, k, v, decay_logits, removal_logits, gate_logits, state)
+    _f32(decay_bias, removal_bias, norm_weight, state)
+    _check_i32(q_cu, positions, state_slots)
+    rows, n = r.shape
+    assert n == n_heads * head_dim
+    ld = r.stride(0)
+    for t in (r, k, v, removal_logits, gate_logits):
+        assert t.shape == (rows, n) and t.stride(1) == 1 and t.stride(0) == ld and t.dtype == r.dtype
+    assert decay_logits.shape == (rows, n) and decay_logits.stride(1) == 1 and decay_logits.dtype == r.dtype
+    assert state.shape[1:] == (n_heads, head_dim, head_dim)
+    out = torch.empty((rows, n), dtype=r.dtype, device=r.device)
+    check(_lib.load().b200_delta_rule(_p(out), n, _p(r), _p(k), _p(v), _p(decay_logits), _p(removal_logits),
+                                      _p(gate_logits), ld, decay_logits.stride(0), _p(decay_bias),
+                                      _p(removal_bias), _p(norm_weight), _p(state), _p(q_cu), _p(positions),
+                                      _p(state_slots), state_slots.numel(), n_heads, head_dim, decay_scale,
+                                      key_eps, eps, _dt(r), _stream()))
+    return out
+
+
+# ---------------------------------------------------------------------------
+# mixture of experts (csrc/moe.cu)
+# ---------------------------------------------------------------------------
+def moe_route(h: torch.Tensor, router_weight: torch.Tensor, top: int) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Sigmoid router in fp32: (expert ids [rows, top] int32, routing weights [rows, top] fp32)."""
+    _cuda(h, router_weight)
+    _f32(router_weight)
+    rows, W = h.shape
+    E = router_weight.shape[0]
+    assert h.stride(1) == 1 and router_weight.shape[1] == W
+    ids = torch.empty((rows, top), dtype=torch.int32, device=h.device)
+    wts = torch.empty((rows, top), dtype=torch.float32, device=h.device)
+    check(_lib.load().b200_moe_route(_p(ids), _p(wts), _p(h), h.stride(0), _p(router_weight), rows, W, E, top,
+                                     _dt(h), _stream()))
+    return ids, wts
+
+
+def moe_plan(expert_ids: torch.Tensor, n_experts: int) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    """(offsets [E + 1], sorted_pair [n], pos_of_pair [n]) of the (token, choice) pairs grouped by expert."""
+    _cuda(expert_ids)
+    _check_i32(expert_ids)
+    n = expert_ids.numel()
+    dev = expert_ids.device
+    offsets = torch.empty(n_experts + 1, dtype=torch.int32, device=dev)
+    sorted_pair = torch.empty(n, dtype=torch.int32, device=dev)
+    pos_of_pair = torch.empty(n, dtype=torch.int32, device=dev)
+    check(_lib.load().b200_moe_plan(_p(offsets), _p(sorted_pair), _p(pos_of_pair), _p(expert_ids), n, n_experts,
+                                    _stream()))
+    return offsets, sorted_pair, pos_of_pair
+
+
+def grouped_gemm(a: torch.Tensor, weights: torch.Tensor, offsets: torch.Tensor, n_rows: int,
+                 sorted_pair: Optional[torch.Tensor] = None, pair_scale: Optional[torch.Tensor] = None,
+                 top: int = 1) -> torch.Tensor:
+    """C[pos] = A(pos) @ weights[e]^T for the sorted positions pos of every expert e (offsets).
+    With sorted_pair, A(pos) = pair_scale[pair] * a[pair // top] (gather form); else A(pos) = a[pos]."""
+    _cuda(a, weights)
+    _check_i32(offsets)
+    E, N, K = weights.shape
+    assert weights.is_contiguous() and a.dim() == 2 and a.shape[1] == K and a.stride(1) == 1
+    assert a.dtype == weights.dtype and offsets.numel() == E + 1
+    if sorted_pair is not None:
+        _check_i32(sorted_pair)
+        _f32(pair_scale)
+    out = torch.empty((n_rows, N), dtype=a.dtype, device=a.device)
+    check(_lib.load().b200_grouped_gemm(_p(out), N, _p(a), a.stride(0), _p(sorted_pair), _p(pair_scale), top,
+                                        _p(weights), _p(offsets), n_rows, E, N, K, _dt(a), _stream()))
+    return out
+
+
+def moe_combine(y: torch.Tensor, pos_of_pair: torch.Tensor, rows: int, top: int) -> torch.Tensor:
+    _cuda(y)
+    _check_i32(pos_of_pair)
+    assert y.dim() == 2 and y.stride(1) == 1 and pos_of_pair.numel() == rows * top
+    out = torch.empty((rows, y.shape[1]), dtype=y.dtype, device=y.device)
+    check(_lib.load().b200_moe_combine(_p(out), _p(y), y.stride(0), _p(pos_of_pair), rows, y.shape[1], top,
+                                       _dt(y), _stream()))
+    return out

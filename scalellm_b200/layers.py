@@ -41,12 +41,17 @@ class InputParameters:
     new_cache_slots: Optional[torch.Tensor] = None  # int32 [n_tokens]
     block_tables: Optional[torch.Tensor] = None     # int32 [n_blocks] first-slot ids (batch.cpp:206-209)
     cu_block_lens: Optional[torch.Tensor] = None    # int32 [n_seq+1]
+    # models with per-sequence recurrent state (token shift, delta rule): which packed row belongs to
+    # which sequence of the step, and the state slot of every sequence
+    token_seq: Optional[torch.Tensor] = None        # int32 [n_tokens]
+    state_slots: Optional[torch.Tensor] = None      # int32 [n_seq]
 
     def to(self, device) -> "InputParameters":
         mv = lambda t: None if t is None else t.to(device)
         return InputParameters(self.num_sequences, mv(self.q_cu_seq_lens), mv(self.kv_cu_seq_lens),
                                self.kv_max_seq_len, self.q_max_seq_len, mv(self.new_cache_slots),
-                               mv(self.block_tables), mv(self.cu_block_lens))
+                               mv(self.block_tables), mv(self.cu_block_lens), mv(self.token_seq),
+                               mv(self.state_slots))
 
 
 class KVCache:
@@ -95,6 +100,24 @@ def apply_llama3_rope_scaling(inv_freq: torch.Tensor, factor: float, low_freq_fa
     mid = (1 - smooth) * f / factor + smooth * f
     out = torch.where(wavelen < high_wl, f, torch.where(wavelen > low_wl, f / factor, mid))
     return out.to(torch.float32)
+
+
+def apply_yarn_rope_scaling(inv_freq: torch.Tensor, base: float, rotary_dim: int, factor: float,
+                            original_len: float, fast: float, slow: float) -> Tuple[torch.Tensor, float]:
+    """YaRN: frequencies whose wavelength fits the original context `slow` times or fewer are divided by
+    `factor`, those that fit it `fast` times or more are kept, with a linear ramp over the pair index
+    in between.  Returns (inv_freq, multiplier of cos and sin = 0.1 ln(factor) + 1).  Evaluated in
+    float64 and rounded once to float32."""
+    f = inv_freq.to(torch.float64)
+
+    def pair_index(turns: float) -> float:   # the pair that makes `turns` full turns over original_len
+        return rotary_dim * math.log(original_len / (2.0 * math.pi * turns)) / (2.0 * math.log(base))
+    lo = max(math.floor(pair_index(fast)), 0)
+    hi = min(math.ceil(pair_index(slow)), rotary_dim - 1)
+    i = torch.arange(f.numel(), dtype=torch.float64)
+    ramp = ((i - lo) / max(hi - lo, 0.001)).clamp(0.0, 1.0)
+    out = f / factor * ramp + f * (1.0 - ramp)
+    return out.to(torch.float32), 0.1 * math.log(factor) + 1.0
 
 
 class RotaryEmbedding:
@@ -562,5 +585,194 @@ class RowParallelLinear:
             x = scatter_to_model_parallel_region(x, self.pa)
         out = _dense_linear(x, self.weight)
         return reduce_from_model_parallel_region(out, self.pa)
+
+    __call__ = forward
+
+
+# ---------------------------------------------------------------------------
+# layers of decoders with several fp32 residual streams, latent attention, delta-rule mixers and
+# token-choice experts (kernels: csrc/hyper.cu, latent_attn.cu, delta_rule.cu, moe.cu).  The
+# reference has no such layers; each class states its arithmetic.  Small vectors (norm weights,
+# biases, stream coefficients, router weights) are kept in fp32 whatever the model dtype is.
+# ---------------------------------------------------------------------------
+class Linear:
+    """Unsharded y = x W^T in the model dtype, W [out, in].  bf16 with at most _DENSE_PREFILL_ROWS
+    rows: the tcgen05 stream kernel where the library has it and the shape fits; otherwise the
+    library GEMM (fp32 weights: true fp32, TF32 is never enabled here)."""
+
+    def __init__(self, weight: torch.Tensor):
+        assert weight.dim() == 2
+        self.weight = weight.contiguous()
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        if x.shape[0] <= _DENSE_PREFILL_ROWS:
+            return _dense_linear(x, self.weight)
+        return F.linear(x, self.weight)
+
+    __call__ = forward
+
+
+class LatentKVCache:
+    """One row [latent (rank) | rotary key (rot_dim)] per cached token: [n_blocks * block_size, rank + rot_dim]."""
+
+    def __init__(self, n_blocks: int, block_size: int, rank: int, rot_dim: int, dtype: torch.dtype, device):
+        self._block_size = block_size
+        self.rows = torch.zeros((n_blocks * block_size, rank + rot_dim), dtype=dtype, device=device)
+
+    def block_size(self) -> int:
+        return self._block_size
+
+
+class HyperConnection:
+    """Reads a sublayer's input from S residual streams and writes its result back:
+        read   u = sum_s a[s] x_s ;  n = u / rms(u) * (offset + w)
+        write  x_t <- sum_s M[s, t] x_s + b[t] * y * sigmoid(G n + c)        (G absent: no gate)
+    S = 1 with a = b = M = 1 is the ordinary pre-norm residual.  X is fp32 [rows, S, W]."""
+
+    def __init__(self, norm_weight: torch.Tensor, eps: float, norm_offset: float,
+                 collapse: Optional[torch.Tensor], mix: Optional[torch.Tensor],
+                 out_coef: Optional[torch.Tensor], gate: Optional[Linear], gate_bias: Optional[torch.Tensor],
+                 dtype: torch.dtype):
+        f = lambda t: None if t is None else t.to(torch.float32).contiguous()
+        self.norm_weight, self.eps, self.norm_offset = f(norm_weight), eps, norm_offset
+        self.collapse, self.mix, self.out_coef = f(collapse), f(mix), f(out_coef)
+        self.gate, self.gate_bias, self.dtype = gate, f(gate_bias), dtype
+
+    def read(self, X: torch.Tensor, want_fp32: bool = False):
+        return kernels.hc_norm(X, self.collapse, self.norm_weight, self.eps, self.norm_offset, self.dtype,
+                               want_fp32)
+
+    def write(self, X: torch.Tensor, y: torch.Tensor, n: torch.Tensor) -> None:
+        g = self.gate(n) if self.gate is not None else None
+        kernels.gated_hc_update(X, y, g, self.gate_bias, self.mix, self.out_coef)
+
+
+class TokenShift:
+    """h_t = n_t + (n_{t-1} - n_t) * mu, with the last unshifted row of every sequence kept in a state slot."""
+
+    def __init__(self, mu: torch.Tensor, n_slots: int, dtype: torch.dtype, device):
+        self.mu = mu.to(torch.float32).contiguous()
+        self.state = torch.zeros((n_slots, mu.numel()), dtype=torch.float32, device=device)
+        self.dtype = dtype
+
+    def forward(self, n32: torch.Tensor, positions: torch.Tensor, params: InputParameters) -> torch.Tensor:
+        return kernels.token_shift(n32, self.mu, self.state, params.q_cu_seq_lens, positions, params.token_seq,
+                                   params.state_slots, self.dtype)
+
+    __call__ = forward
+
+
+class LatentAttention:
+    """Attention with keys and values compressed into one latent per token:
+        q = Wq h (per head [dim | rot_dim]) ; [c_raw | kr_raw] = Wdkv h
+        c = rmsnorm(c_raw) * wc ; kr = rope(kr_raw), one rotary key part for all heads ; rope(q rotary part)
+        k_h = Uk_h c ; v_h = Uv_h c ; s = (q_h[:dim] . k_h + q_h[dim:] . kr) * scale ; causal softmax
+        out = Wo (concat_h(sum_j p_j v_hj) (* sigmoid(Wg h) when there is an output gate))
+    Only [c | kr] is cached (LatentKVCache).  The key map is folded into the query and the value map is
+    applied after the weighted sum of latents, so the attention kernel runs in the latent space."""
+
+    def __init__(self, w: Dict[str, torch.Tensor], n_heads: int, dim: int, rot_dim: int, vdim: int, rank: int,
+                 scale: float, inv_freq: torch.Tensor, rot_mult: float, rot_dims: int, eps: float,
+                 dtype: torch.dtype, device):
+        self.H, self.dim, self.rd, self.vd, self.rank = n_heads, dim, rot_dim, vdim, rank
+        self.scale, self.rot_mult, self.rot_dims, self.eps, self.dtype = scale, rot_mult, rot_dims, eps, dtype
+        self.inv_freq = inv_freq.to(torch.float32).to(device).contiguous()
+        qw = H_dq = n_heads * (dim + rot_dim)
+        parts = [w["q"], w["dkv"]] + ([w["g"]] if "g" in w else [])
+        self.has_gate = "g" in w
+        self.in_proj = Linear(torch.cat(parts, dim=0))          # one GEMM for everything that reads h
+        self.q_end, self.dkv_end = qw, qw + rank + rot_dim
+        self.c_norm = w["dkv.norm"].to(torch.float32).contiguous()
+        self.uk = w["uk"].reshape(n_heads, dim, rank).contiguous()               # [H, dim, rank]
+        self.uv_t = w["uv"].reshape(n_heads, vdim, rank).transpose(1, 2).contiguous()   # [H, rank, vdim]
+        self.o_proj = Linear(w["o"])
+        del H_dq
+
+    def forward(self, h: torch.Tensor, positions: torch.Tensor, cache: LatentKVCache,
+                params: InputParameters) -> torch.Tensor:
+        T = h.shape[0]
+        H, dim, rd, rank = self.H, self.dim, self.rd, self.rank
+        proj = self.in_proj(h)
+        q, dkv = proj[:, : self.q_end], proj[:, self.q_end: self.dkv_end]
+        kernels.latent_prepare(q, dkv, cache.rows, self.c_norm, self.inv_freq, self.rot_mult, positions,
+                               params.new_cache_slots, H, dim, rd, self.rot_dims, rank, self.eps)
+        qu = q.view(T, H, dim + rd)[:, :, :dim].transpose(0, 1)                 # [H, T, dim] (strided view)
+        if self.dtype == torch.float32:
+            qa = torch.bmm(qu, self.uk)
+        else:   # keep the folded query in fp32: scores are formed in fp32 from it
+            qa = torch.bmm(qu.contiguous(), self.uk, out_dtype=torch.float32)
+        lat = kernels.latent_attn(qa, q, cache.rows, params.q_cu_seq_lens, params.kv_cu_seq_lens,
+                                  params.block_tables, params.cu_block_lens, params.token_seq, H, dim, rd, rank,
+                                  cache.block_size(), self.scale)
+        o = torch.bmm(lat, self.uv_t)                                           # [H, T, vdim]
+        o = kernels.heads_to_rows(o, proj[:, self.dkv_end:] if self.has_gate else None)
+        return self.o_proj(o)
+
+    __call__ = forward
+
+
+class DeltaRuleMixer:
+    """Generalised delta rule (csrc/delta_rule.cu): r, k, v, output gate and removal logits are
+    projections of h; the decay logits come through a low-rank pair W2 tanh(W1 h).  The recurrent
+    state [n_slots, H, d, d] is fp32."""
+
+    def __init__(self, w: Dict[str, torch.Tensor], n_heads: int, head_dim: int, decay_scale: float,
+                 key_eps: float, eps: float, n_slots: int, dtype: torch.dtype, device):
+        self.H, self.d, self.dtype = n_heads, head_dim, dtype
+        self.decay_scale, self.key_eps, self.eps = decay_scale, key_eps, eps
+        self.n = n_heads * head_dim
+        self.in_proj = Linear(torch.cat([w["r"], w["k"], w["v"], w["g"], w["a"], w["w1"]], dim=0))
+        self.w2 = Linear(w["w2"])
+        f = lambda t: t.to(torch.float32).contiguous()
+        self.w0, self.a0, self.norm_weight = f(w["w0"]), f(w["a.b"]), f(w["norm"])
+        self.o_proj = Linear(w["o"])
+        self.state = torch.zeros((n_slots, n_heads, head_dim, head_dim), dtype=torch.float32, device=device)
+
+    def forward(self, h: torch.Tensor, positions: torch.Tensor, params: InputParameters) -> torch.Tensor:
+        n = self.n
+        proj = self.in_proj(h)
+        r, k, v, g, a = (proj[:, i * n:(i + 1) * n] for i in range(5))
+        wl = self.w2(torch.tanh(proj[:, 5 * n:]))
+        o = kernels.delta_rule(r, k, v, wl, a, g, self.w0, self.a0, self.norm_weight, self.state,
+                               params.q_cu_seq_lens, positions, params.state_slots, self.H, self.d,
+                               self.decay_scale, self.key_eps, self.eps)
+        return self.o_proj(o)
+
+    __call__ = forward
+
+
+class GatedMLP:
+    """down(act(gate h) * (up h)); act "silu" or "gelu_tanh".  gate and up share one GEMM."""
+
+    def __init__(self, gate: torch.Tensor, up: torch.Tensor, down: torch.Tensor, act: str):
+        self.gate_up, self.down, self.act = Linear(torch.cat([gate, up], dim=0)), Linear(down), act
+
+    def forward(self, h: torch.Tensor) -> torch.Tensor:
+        return self.down(kernels.gated_act(self.gate_up(h), self.act))
+
+    __call__ = forward
+
+
+class SparseMoE:
+    """Token-choice experts with a sigmoid router: s = sigmoid(Wr h) in fp32, the `top` largest are chosen,
+    the routing weight is s (not renormalised) and scales the expert's INPUT:
+        out = sum over chosen e of down_e(act(gate_e x) * (up_e x)),  x = s_e * h.
+    Expert weights are stacked [E, ...]; pairs are grouped by expert on the device (no host sync)."""
+
+    def __init__(self, router: torch.Tensor, gate: torch.Tensor, up: torch.Tensor, down: torch.Tensor,
+                 top: int, act: str):
+        self.router = router.to(torch.float32).contiguous()
+        self.gate_up = torch.cat([gate, up], dim=1).contiguous()     # [E, 2 ff, W]
+        self.down = down.contiguous()                                  # [E, W, ff]
+        self.E, self.top, self.act = router.shape[0], top, act
+
+    def forward(self, h: torch.Tensor) -> torch.Tensor:
+        rows = h.shape[0]
+        ids, wts = kernels.moe_route(h, self.router, self.top)
+        offsets, sorted_pair, pos_of_pair = kernels.moe_plan(ids, self.E)
+        n = rows * self.top
+        gu = kernels.grouped_gemm(h, self.gate_up, offsets, n, sorted_pair, wts.view(-1), self.top)
+        y = kernels.grouped_gemm(kernels.gated_act(gu, self.act), self.down, offsets, n)
+        return kernels.moe_combine(y, pos_of_pair, rows, self.top)
 
     __call__ = forward
