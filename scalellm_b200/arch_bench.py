@@ -1,0 +1,214 @@
+"""Prefill and decode throughput of the Kigalix design beside the Llama decoder at equal size
+(`bench.py --arch kigalix`), both through the serving engine, random weights, bf16.
+
+Per size: tokens/s of a prompt step (B sequences of L tokens in one batch) and of decode steps (B sequences
+with L cached tokens, one token each), timed with CUDA events after warm-up; and, per kind of kernel, the
+device time per step (events around every call of the kernel wrappers) with its algorithmic bytes and FLOPs
+against the measured copy bandwidth and bf16 GEMM throughput.  Weights and caches are larger than L2 at the
+larger size; the smaller one says so in its line.
+"""
+from __future__ import annotations
+
+import json
+import os
+import time
+from typing import Callable, Dict, List
+
+import torch
+
+SIZES = {
+    # width, layers, attention heads x (dim + rot), latent rank, value size, delta heads x dim, dense ff, experts
+    "w2048": dict(width=2048, layers=4, heads=16, dim=128, rot=64, vdim=128, rank=512, dheads=32, ddim=64,
+                  ff=5632, experts=8, top=2, eff=1408, vocab=32000),
+    "w4096": dict(width=4096, layers=4, heads=32, dim=128, rot=64, vdim=128, rank=512, dheads=64, ddim=64,
+                  ff=11008, experts=8, top=2, eff=2752, vocab=32000),
+}
+
+
+def kigalix_config(s: dict) -> dict:
+    rot = {"base": 10000.0, "dims": s["rot"]}
+    yarn = dict(rot, scaling={"factor": 8.0, "original": 4096, "fast": 32.0, "slow": 1.0})
+    scale = (s["dim"] + s["rot"]) ** -0.5
+    la = lambda kind, r: {"type": kind, "mixer": {"heads": s["heads"], "dim": s["dim"], "rot_dim": s["rot"],
+                                                   "vdim": s["vdim"], "kv_rank": s["rank"], "rot": r, "scale": scale}}
+    dl = {"type": "general_delta", "mixer": {"heads": s["dheads"], "dim": s["ddim"]}}
+    moe = {"kind": "moe", "expert": {"ff": s["eff"]}, "router": {"experts": s["experts"], "top": s["top"]}}
+    pattern = [dict(la("latent_attention_2", yarn), mlp={"kind": "dense", "ff": s["ff"]}), dict(dl, mlp=moe),
+               dict(la("latent_attention", rot), mlp=moe), dict(la("latent_attention", rot), mlp=moe)]
+    return {"architecture": "Kigalix", "width": s["width"], "vocab": s["vocab"], "streams": 2,
+            "norm": {"eps": 1e-5}, "layers": [pattern[i % 4] for i in range(s["layers"])]}
+
+
+def llama_config(s: dict) -> dict:
+    return {"architectures": ["LlamaForCausalLM"], "hidden_size": s["width"], "num_hidden_layers": s["layers"],
+            "num_attention_heads": s["width"] // 128, "num_key_value_heads": max(1, s["width"] // 512),
+            "intermediate_size": s["ff"], "vocab_size": s["vocab"], "rope_theta": 10000.0, "rms_norm_eps": 1e-5,
+            "max_position_embeddings": 8192, "rope_scaling": None}
+
+
+class KernelTimer:
+    """Wraps functions of a module so that every call is bracketed by CUDA events on the current stream."""
+
+    def __init__(self):
+        self.events: Dict[str, List] = {}
+        self._undo: List = []
+
+    def wrap(self, owner, names: List[str], label: Callable[[str], str] = lambda n: n) -> None:
+        for n in names:
+            fn = getattr(owner, n)
+
+            def timed(*a, __fn=fn, __l=label(n), **k):
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                out = __fn(*a, **k)
+                e1.record()
+                self.events.setdefault(__l, []).append((e0, e1))
+                return out
+            self._undo.append((owner, n, fn))
+            setattr(owner, n, timed)
+
+    def restore(self) -> None:
+        for owner, n, fn in self._undo:
+            setattr(owner, n, fn)
+        self._undo = []
+
+    def totals_ms(self) -> Dict[str, float]:
+        torch.cuda.synchronize()
+        out = {k: sum(a.elapsed_time(b) for a, b in v) for k, v in self.events.items()}
+        self.events = {}
+        return out
+
+
+def _time_steps(fn: Callable[[], None], warmup: int, steps: int) -> float:
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / steps
+
+
+def _run_model(config: dict, batch: int, seqlen: int, warmup: int, steps: int, kernel_names, seed: int = 0):
+    from . import kernels, registry
+    from .engine import Engine, StepEntry
+    dev = torch.device("cuda", torch.cuda.current_device())
+    model = registry.create_model(config, torch.bfloat16, dev, max_seqs=batch)
+    model.init_random(seed)
+    bs = 16
+    eng = Engine(model, max_tokens=batch * (seqlen + 64 + bs), block_size=bs, max_seqs=batch,
+                 max_step_tokens=batch * seqlen)
+    g = torch.Generator().manual_seed(seed)
+    V = config.get("vocab", config.get("vocab_size"))
+    prompts = [[int(x) for x in torch.randint(0, V, (seqlen,), generator=g)] for _ in range(batch)]
+    res = {}
+
+    def prefill():
+        eng.step([StepEntry(f"s{i}", p, [len(p) - 1]) for i, p in enumerate(prompts)])
+
+    def reset():
+        for rid in list(eng.seqs):
+            eng.finish(rid)
+
+    # prompt steps: every timed step admits the batch afresh (blocks and slots are reused)
+    def prefill_once():
+        reset()
+        prefill()
+    ms = _time_steps(prefill_once, min(warmup, 2), max(2, min(steps, 5)))
+    res["prefill"] = {"ms_per_step": ms, "tokens_per_s": batch * seqlen / ms * 1e3}
+    reset()
+    prefill()
+
+    def decode():
+        eng.step([StepEntry(f"s{i}", [7], [0]) for i in range(batch)])
+    ms = _time_steps(decode, warmup, min(steps, 48))
+    res["decode"] = {"ms_per_step": ms, "tokens_per_s": batch / ms * 1e3}
+    # per-kernel device time of one prompt step and one decode step
+    timer = KernelTimer()
+    timer.wrap(kernels, kernel_names)
+    timer.wrap(kernels, ["dense_gemm"], lambda n: "linear (dense GEMMs)")
+    timer.wrap(torch.nn.functional, ["linear"], lambda n: "linear (dense GEMMs)")
+    timer.wrap(torch, ["bmm"], lambda n: "bmm (per-head key / value maps)")
+    try:
+        decode()
+        res["decode"]["kernels_ms"] = timer.totals_ms()
+        prefill_once()
+        res["prefill"]["kernels_ms"] = timer.totals_ms()
+    finally:
+        timer.restore()
+    reset()
+    del eng, model
+    torch.cuda.empty_cache()
+    return res
+
+
+KIGALIX_KERNELS = ["embed_streams", "hc_norm", "token_shift", "gated_hc_update", "gated_act", "heads_to_rows",
+                   "latent_prepare", "latent_attn", "delta_rule", "moe_route", "moe_plan", "grouped_gemm", "moe_combine"]
+LLAMA_KERNELS = ["rms_norm", "rms_norm_residual", "rope_and_set_kv_cache", "paged_kv_varlen_mha", "silu_mul",
+                 "silu_with_mul", "apply_rotary_pos_emb", "set_kv_cache"]
+
+
+def rooflines(s: dict, batch: int, seqlen: int, k: dict, l: dict, peaks: dict) -> dict:
+    """Achieved fraction of the nearer roof (copy bandwidth or bf16 GEMM rate) for the attention kernels of
+    both models and the expert GEMMs, from the per-kernel times of one step."""
+    hbm, tf = peaks["hbm_gbs"] * 1e9, peaks["bf16_tflops"] * 1e12
+    n_lat = sum(1 for i in range(s["layers"]) if i % 4 != 1)
+    n_moe = sum(1 for i in range(s["layers"]) if i % 4 != 0)
+    Dk, out = s["rank"] + s["rot"], {}
+
+    def frac(ms, nbytes, flops):
+        t = ms * 1e-3
+        return {"ms": ms, "of_copy_peak": nbytes / t / hbm, "of_gemm_peak": flops / t / tf,
+                "roof_ms": max(nbytes / hbm, flops / tf) * 1e3, "of_roof": max(nbytes / hbm, flops / tf) / t}
+    for phase, keys in (("decode", batch * (seqlen + 1)), ("prefill", batch * seqlen * (seqlen + 1) // 2)):
+        rows = batch if phase == "decode" else batch * seqlen
+        cached = batch * (seqlen + (1 if phase == "decode" else 0))
+        ms = k[phase]["kernels_ms"].get("latent_attn", 0.0)
+        out[f"kigalix latent_attn {phase}"] = frac(ms, n_lat * (cached * Dk * 2 + rows * s["heads"] * (Dk + s["rank"]) * 4),
+                                                  n_lat * keys * s["heads"] * 2 * (Dk + s["rank"]))
+        H, Hkv = s["width"] // 128, max(1, s["width"] // 512)
+        ms = l[phase]["kernels_ms"].get("paged_kv_varlen_mha", 0.0)
+        out[f"llama paged attention {phase}"] = frac(ms, s["layers"] * (cached * 2 * Hkv * 128 * 2 + rows * H * 128 * 4),
+                                                     s["layers"] * keys * H * 4 * 128)
+        pairs = rows * s["top"]
+        ms = k[phase]["kernels_ms"].get("grouped_gemm", 0.0)
+        out[f"kigalix expert GEMMs {phase}"] = frac(ms, n_moe * (s["experts"] * 3 * s["eff"] * s["width"] * 2
+                                                              + pairs * (s["width"] * 2 + 3 * s["eff"]) * 2),
+                                                   n_moe * pairs * 6 * s["eff"] * s["width"])
+        ms = l[phase]["kernels_ms"].get("linear (dense GEMMs)", 0.0)
+        wbytes = s["layers"] * (s["width"] * (s["width"] + 2 * max(1, s["width"] // 512) * 128) + s["width"] * s["width"]
+                                + 3 * s["ff"] * s["width"]) * 2
+        nlog = batch
+        out[f"llama dense GEMMs {phase}"] = frac(ms, wbytes + s["vocab"] * s["width"] * 2,
+                                                 (wbytes // 2) * 2 * rows + nlog * 2 * s["vocab"] * s["width"])
+        ms = k[phase]["kernels_ms"].get("delta_rule", 0.0)
+        n_d = s["layers"] - n_lat
+        dn = s["dheads"] * s["ddim"]
+        out[f"kigalix delta_rule {phase}"] = frac(ms, n_d * (rows * 7 * dn * 2 + batch * 2 * dn * s["ddim"] * 4),
+                                                  n_d * rows * s["dheads"] * 6 * s["ddim"] ** 2)
+    return out
+
+
+def run(args) -> None:
+    torch.cuda.set_device(0)
+    torch.backends.cuda.matmul.allow_tf32 = False
+    peaks_path = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "MEASURED_PEAKS.json")
+    peaks = json.load(open(peaks_path)) if os.path.exists(peaks_path) else {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
+    out = {"metric": "kigalix_vs_llama_tokens_per_s", "unit": "tokens/s", "dtype": "bf16",
+           "data": "synthetic (random-init weights, random token ids)", "n_gpus": 1,
+           "peaks": {"hbm_gbs": peaks["hbm_gbs"], "bf16_tflops": peaks["bf16_tflops"],
+                     "source": "measured" if os.path.exists(peaks_path) else "fallback"}, "sizes": {}}
+    names = [args.arch_size] if args.arch_size != "all" else list(SIZES)
+    for name in names:
+        s = SIZES[name]
+        batch, seqlen = args.arch_batch, args.arch_seqlen
+        t0 = time.time()
+        k = _run_model(kigalix_config(s), batch, seqlen, args.warmup, args.steps, KIGALIX_KERNELS)
+        l = _run_model(llama_config(s), batch, seqlen, args.warmup, args.steps, LLAMA_KERNELS)
+        out["sizes"][name] = {"shape": s, "batch": batch, "seq_len": seqlen, "kigalix": k, "llama": l,
+                              "kernel_rooflines": rooflines(s, batch, seqlen, k, l, peaks),
+                              "seconds": round(time.time() - t0, 1)}
+    print(json.dumps(out))

@@ -27,6 +27,7 @@ from .layers import (Attention, B200AttnHandler, ColumnParallelLinear, ColumnPar
                      InputParameters, KVCache, QuantArgs, RMSNorm, RowParallelLinear,
                      RowParallelQLinear, apply_llama3_rope_scaling, compute_default_inv_freq)
 from .model_parallel import (ParallelArgs, gather_from_model_parallel_region, local_heads)
+from .registry import register_model
 
 
 @dataclass
@@ -66,7 +67,50 @@ def _inv_freq(args: LlamaArgs) -> torch.Tensor:
     return f
 
 
+@register_model("llama", "LlamaForCausalLM")
 class LlamaDecoder:
+    needs_state_slots = False
+    CSRC = ("elementwise.cu", "paged_attn.cu", "prefill_attn.cu", "dense.cu", "w4a16.cu")
+
+    # -- the registry's interface (unquantised bf16 checkpoints with Hugging Face tensor names) ---------
+    @classmethod
+    def from_config(cls, config: dict, dtype, device, max_seqs: int = 4) -> "LlamaDecoder":
+        """config.json keys as in models/meta/llama.h:341-406 (hidden_size, num_hidden_layers, ...)."""
+        if dtype != torch.bfloat16:
+            raise ValueError("the Llama path runs in bfloat16")
+        h, nh = int(config["hidden_size"]), int(config["num_attention_heads"])
+        args = LlamaArgs(hidden_size=h, n_layers=int(config["num_hidden_layers"]), n_heads=nh,
+                         n_kv_heads=int(config.get("num_key_value_heads", nh)),
+                         head_dim=int(config.get("head_dim", h // nh)),
+                         intermediate_size=int(config["intermediate_size"]), vocab_size=int(config["vocab_size"]),
+                         rope_theta=float(config.get("rope_theta", 10000.0)),
+                         rms_norm_eps=float(config.get("rms_norm_eps", 1e-5)),
+                         max_position_embeddings=int(config.get("max_position_embeddings", 8192)),
+                         rope_scaling=config.get("rope_scaling"))
+        return cls(args, QuantArgs(), ParallelArgs(0, 1, None), torch.device(device), dtype)
+
+    @property
+    def n_vocab(self) -> int:
+        return self.args.vocab_size
+
+    def alloc_cache(self, n_blocks: int, block_size: int) -> None:
+        self.alloc_kv(n_blocks, block_size, randomize=False)
+
+    def load_weights(self, tensors: Dict[str, torch.Tensor]) -> None:
+        t = lambda n: tensors[n].to(self.device).to(self.dtype)
+        for i in range(self.args.n_layers):
+            p = f"model.layers.{i}."
+            a, m = p + "self_attn.", p + "mlp."
+            self.load_layer(i, {
+                "qkv": {"weight": torch.cat([t(a + "q_proj.weight"), t(a + "k_proj.weight"), t(a + "v_proj.weight")])},
+                "o": {"weight": t(a + "o_proj.weight")},
+                "gate_up": {"weight": torch.cat([t(m + "gate_proj.weight"), t(m + "up_proj.weight")])},
+                "down": {"weight": t(m + "down_proj.weight")},
+                "input_norm": t(p + "input_layernorm.weight"), "post_norm": t(p + "post_attention_layernorm.weight")})
+        self.embed.copy_(t("model.embed_tokens.weight"))
+        self.final_norm.weight.copy_(t("model.norm.weight"))
+        self.lm_head.weight.copy_(t("lm_head.weight" if "lm_head.weight" in tensors else "model.embed_tokens.weight"))
+
     def __init__(self, args: LlamaArgs, qa: QuantArgs, pa: ParallelArgs, device,
                  dtype: torch.dtype = torch.bfloat16):
         self.args, self.qa, self.pa, self.device, self.dtype = args, qa, pa, device, dtype
