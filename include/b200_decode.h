@@ -515,7 +515,12 @@ B200_API int b200_latent_attn(void* out, int64_t out_head_stride, int64_t out_to
                               int64_t ldq, const void* cache, int64_t ldc, const int32_t* q_cu_lens,
                               const int32_t* kv_cu_lens, const int32_t* block_tables, const int32_t* cu_block_lens,
                               const int32_t* token_seq, int64_t rows, int64_t H, int64_t dim, int64_t rd,
-                              int64_t rank, int64_t block_size, float scale, int dtype, b200_stream_t stream);
+                              int64_t rank, int64_t block_size, float scale, int n_splits, void* workspace,
+                              int64_t workspace_bytes, int dtype, b200_stream_t stream);
+/* n_splits >= 1 (bf16 only): tensor-core form, the keys of every row cut into n_splits ranges that run as
+ * separate CTAs and are merged by a second kernel (n_splits > 1 needs the workspace below); n_splits = 0: the
+ * CUDA-core form (any dtype, fp32 arithmetic throughout). */
+B200_API int64_t b200_latent_attn_workspace_bytes(int64_t rows, int64_t H, int64_t rank, int64_t n_splits);
 /* Generalised delta rule over each sequence's tokens of the step (see delta_rule.cu); r, k, v, removal and gate
  * logits are column blocks [H * d] of matrices with row stride ld, the decay logits have row stride ld_decay;
  * state fp32 [n_slots, H, d, d]. */

@@ -105,7 +105,8 @@ SIGNATURES = {
     "b200_latent_prepare": (_int, [_vp, _i64, _vp, _i64, _vp, _i64, _vp, _vp, _f32, _vp, _vp, _i64, _i64,
                                    _i64, _i64, _i64, _i64, _f32, _int, _vp]),
     "b200_latent_attn": (_int, [_vp, _i64, _i64, _vp, _i64, _i64, _int, _vp, _i64, _vp, _i64, _vp, _vp, _vp,
-                                _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i64, _f32, _int, _vp]),
+                                _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i64, _f32, _int, _vp, _i64, _int, _vp]),
+    "b200_latent_attn_workspace_bytes": (_i64, [_i64, _i64, _i64, _i64]),
     "b200_delta_rule": (_int, [_vp, _i64, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _vp, _vp, _vp, _vp, _vp,
                                _vp, _vp, _i64, _i64, _i64, _f32, _f32, _f32, _int, _vp]),
     "b200_moe_route": (_int, [_vp, _vp, _vp, _i64, _vp, _i64, _i64, _i64, _i64, _int, _vp]),

@@ -161,6 +161,8 @@ def rooflines(s: dict, batch: int, seqlen: int, k: dict, l: dict, peaks: dict) -
 
     def frac(ms, nbytes, flops):
         t = ms * 1e-3
+        if t <= 0:
+            return None
         return {"ms": ms, "of_copy_peak": nbytes / t / hbm, "of_gemm_peak": flops / t / tf,
                 "roof_ms": max(nbytes / hbm, flops / tf) * 1e3, "of_roof": max(nbytes / hbm, flops / tf) / t}
     for phase, keys in (("decode", batch * (seqlen + 1)), ("prefill", batch * seqlen * (seqlen + 1) // 2)):

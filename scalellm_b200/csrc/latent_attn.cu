@@ -185,6 +185,287 @@ int dispatch_nr(int rank, void* out, int64_t out_hs, int64_t out_ts, const void*
   return set_error(B200_ERR_UNSUPPORTED, "latent_attn: latent rank %d > 512", rank);
 }
 
+
+// ---------------------------------------------------------------------------------------------
+// Tensor-core form (bf16 cache): one CTA per (token, group of 16 heads, split of the keys), 4 warps.
+// Per 32-key tile: warp w forms S for keys 8w..8w+7 (mma.m16n8k16 over the key width, Q and the
+// tile in shared memory, fragments by ldmatrix), the scaled and masked scores meet in shared memory,
+// every warp redoes the (cheap) online softmax in fp32 and multiplies P by its own quarter of the
+// latent columns (the tile read transposed by ldmatrix.trans).  P enters the tensor core as two
+// bf16 terms, hi + lo, so the weights keep 16 bits of mantissa.  With more than one split each CTA
+// writes an unnormalised partial (fp32) with its running maximum and sum; latent_combine merges them.
+// ---------------------------------------------------------------------------------------------
+constexpr int kMmaRows = 16;
+
+__device__ __forceinline__ void ldsm_x4(uint32_t (&r)[4], const void* p) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_u32(p)));
+}
+__device__ __forceinline__ void ldsm_x4_t(uint32_t (&r)[4], const void* p) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_u32(p)));
+}
+__device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void split_bf16(float x, float y, uint32_t& hi, uint32_t& lo) {
+  const __nv_bfloat16 hx = __float2bfloat16_rn(x), hy = __float2bfloat16_rn(y);
+  hi = Num<__nv_bfloat16>::pack(__bfloat162float(hx), __bfloat162float(hy));
+  lo = Num<__nv_bfloat16>::pack(x - __bfloat162float(hx), y - __bfloat162float(hy));
+}
+
+template <typename QA, int NTV>
+__global__ void __launch_bounds__(128)
+latent_attn_mma_kernel(__nv_bfloat16* __restrict__ out, int64_t out_hs, int64_t out_ts,
+                       float* __restrict__ o_part, float* __restrict__ ml_part, int n_splits,
+                       const QA* __restrict__ qa, int64_t qa_hs, int64_t qa_ts,
+                       const __nv_bfloat16* __restrict__ q, int64_t ldq,
+                       const __nv_bfloat16* __restrict__ cache, int64_t ldc, const int* __restrict__ q_cu,
+                       const int* __restrict__ kv_cu, const int* __restrict__ tables,
+                       const int* __restrict__ blk_cu, const int* __restrict__ token_seq, int rows, int H,
+                       int dim, int rd, int rank, int block_size, float scale) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  const int Dk = rank + rd, DkP = (Dk + 31) / 32 * 32, ld = DkP + 8;
+  __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(smem_raw);   // [16][ld]
+  __nv_bfloat16* Ks = Qs + kMmaRows * ld;                           // [32][ld] + 16 slack
+  float* Ss = reinterpret_cast<float*>(Ks + kTileKeys * ld + 16);   // [16][36]
+  constexpr int lds = 36;
+  const int row = blockIdx.x, hg = blockIdx.y, z = blockIdx.z;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
+  const int seq = token_seq[row];
+  const int q_len = q_cu[seq + 1] - q_cu[seq], kv_len = kv_cu[seq + 1] - kv_cu[seq];
+  const int pos = kv_len - q_len + (row - q_cu[seq]);
+  const int* table = tables + blk_cu[seq];
+  // stage Q: row r of the tile is head hg * 16 + r of this token: [folded query (rank) | rotary part (rd) | 0]
+  for (int idx = tid; idx < kMmaRows * ld; idx += 128) {
+    const int r = idx / ld, d = idx - r * ld, h = hg * kMmaRows + r;
+    float v = 0.0f;
+    if (h < H) {
+      if (d < rank) v = Num<QA>::to_f(qa[(size_t)h * qa_hs + (size_t)row * qa_ts + d]);
+      else if (d < Dk) v = __bfloat162float(q[(size_t)row * ldq + (size_t)h * (dim + rd) + dim + (d - rank)]);
+    }
+    Qs[idx] = __float2bfloat16_rn(v);
+  }
+  const int tiles_total = pos / kTileKeys + 1;
+  const int tps = (tiles_total + n_splits - 1) / n_splits;
+  const int tile0 = z * tps, tile1 = min(tiles_total, tile0 + tps);
+  float acc[NTV][4];
+#pragma unroll
+  for (int i = 0; i < NTV; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.0f;
+  float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.0f, l1 = 0.0f;   // rows g and g + 8
+  const int chunks = ld / 8;                                     // 16-byte chunks of a staged row
+  const int rank8 = (rank + 7) / 8 * 8;
+  for (int tile = tile0; tile < tile1; ++tile) {
+    const int j0 = tile * kTileKeys;
+    __syncthreads();
+    for (int jj = warp; jj < kTileKeys; jj += 4) {
+      const int key = j0 + jj;
+      uint4* dst = reinterpret_cast<uint4*>(Ks + jj * ld);
+      if (key <= pos) {
+        const uint4* src = reinterpret_cast<const uint4*>(cache + ((size_t)table[key / block_size] + key % block_size) * ldc);
+        for (int c = lane; c < chunks; c += 32) dst[c] = (c * 8 < Dk) ? src[c] : make_uint4(0, 0, 0, 0);
+      } else {
+        for (int c = lane; c < chunks; c += 32) dst[c] = make_uint4(0, 0, 0, 0);
+      }
+    }
+    __syncthreads();
+    // S[16 x 8] of this warp's keys
+    float s[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+    for (int k0 = 0; k0 < DkP; k0 += 32) {
+      uint32_t a[4], a2[4], b[4];
+      ldsm_x4(a, Qs + ((lane & 7) + ((lane >> 3) & 1) * 8) * ld + k0 + (lane >> 4) * 8);
+      ldsm_x4(a2, Qs + ((lane & 7) + ((lane >> 3) & 1) * 8) * ld + k0 + 16 + (lane >> 4) * 8);
+      ldsm_x4(b, Ks + (warp * 8 + (lane & 7)) * ld + k0 + (lane >> 3) * 8);
+      mma_bf16(s, a, b[0], b[1]);
+      mma_bf16(s, a2, b[2], b[3]);
+    }
+    {
+      const int key = j0 + warp * 8 + 2 * t;
+      const bool v0 = key <= pos, v1 = key + 1 <= pos;
+      const bool r0 = hg * kMmaRows + g < H, r1 = hg * kMmaRows + g + 8 < H;
+      float* s0 = Ss + g * lds + warp * 8 + 2 * t;
+      float* s1 = Ss + (g + 8) * lds + warp * 8 + 2 * t;
+      s0[0] = (v0 && r0) ? s[0] * scale : -INFINITY;
+      s0[1] = (v1 && r0) ? s[1] * scale : -INFINITY;
+      s1[0] = (v0 && r1) ? s[2] * scale : -INFINITY;
+      s1[1] = (v1 && r1) ? s[3] * scale : -INFINITY;
+    }
+    __syncthreads();
+    // online softmax of rows g and g + 8 (every warp the same), P as A fragments: keys 16 kk + {2t, 2t+1, 2t+8, 2t+9}
+    float p0[8], p1[8];
+#pragma unroll
+    for (int kk = 0; kk < 2; ++kk) {
+#pragma unroll
+      for (int hh = 0; hh < 2; ++hh) {
+        const float2 x0 = *reinterpret_cast<const float2*>(Ss + g * lds + 16 * kk + 8 * hh + 2 * t);
+        const float2 x1 = *reinterpret_cast<const float2*>(Ss + (g + 8) * lds + 16 * kk + 8 * hh + 2 * t);
+        p0[kk * 4 + hh * 2] = x0.x; p0[kk * 4 + hh * 2 + 1] = x0.y;
+        p1[kk * 4 + hh * 2] = x1.x; p1[kk * 4 + hh * 2 + 1] = x1.y;
+      }
+    }
+    float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) { mx0 = fmaxf(mx0, p0[i]); mx1 = fmaxf(mx1, p1[i]); }
+#pragma unroll
+    for (int o = 1; o <= 2; o <<= 1) {
+      mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, o));
+      mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, o));
+    }
+    const float n0 = fmaxf(m0, mx0), n1 = fmaxf(m1, mx1);
+    const float c0 = (n0 == -INFINITY) ? 1.0f : expf(m0 - n0), c1 = (n1 == -INFINITY) ? 1.0f : expf(m1 - n1);
+    float sum0 = 0.0f, sum1 = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      p0[i] = (n0 == -INFINITY) ? 0.0f : expf(p0[i] - n0);
+      p1[i] = (n1 == -INFINITY) ? 0.0f : expf(p1[i] - n1);
+      sum0 += p0[i]; sum1 += p1[i];
+    }
+#pragma unroll
+    for (int o = 1; o <= 2; o <<= 1) {
+      sum0 += __shfl_xor_sync(0xffffffffu, sum0, o);
+      sum1 += __shfl_xor_sync(0xffffffffu, sum1, o);
+    }
+    l0 = l0 * c0 + sum0; l1 = l1 * c1 + sum1; m0 = n0; m1 = n1;
+    uint32_t ph[2][4], pl[2][4];
+#pragma unroll
+    for (int kk = 0; kk < 2; ++kk) {
+      split_bf16(p0[kk * 4 + 0], p0[kk * 4 + 1], ph[kk][0], pl[kk][0]);   // row g,     keys 2t, 2t+1
+      split_bf16(p1[kk * 4 + 0], p1[kk * 4 + 1], ph[kk][1], pl[kk][1]);   // row g + 8
+      split_bf16(p0[kk * 4 + 2], p0[kk * 4 + 3], ph[kk][2], pl[kk][2]);   // row g,     keys 2t+8, 2t+9
+      split_bf16(p1[kk * 4 + 2], p1[kk * 4 + 3], ph[kk][3], pl[kk][3]);
+    }
+#pragma unroll
+    for (int nt = 0; nt < NTV; nt += 2) {
+      const int col0 = (warp * NTV + nt) * 8;
+      if (col0 >= rank8) break;
+      acc[nt][0] *= c0; acc[nt][1] *= c0; acc[nt][2] *= c1; acc[nt][3] *= c1;
+      if (nt + 1 < NTV) { acc[nt + 1][0] *= c0; acc[nt + 1][1] *= c0; acc[nt + 1][2] *= c1; acc[nt + 1][3] *= c1; }
+#pragma unroll
+      for (int kk = 0; kk < 2; ++kk) {
+        uint32_t b[4];
+        ldsm_x4_t(b, Ks + (16 * kk + (lane & 7) + ((lane >> 3) & 1) * 8) * ld + col0 + (lane >> 4) * 8);
+        mma_bf16(acc[nt], ph[kk], b[0], b[1]);
+        mma_bf16(acc[nt], pl[kk], b[0], b[1]);
+        if (nt + 1 < NTV) {
+          mma_bf16(acc[nt + 1], ph[kk], b[2], b[3]);
+          mma_bf16(acc[nt + 1], pl[kk], b[2], b[3]);
+        }
+      }
+    }
+  }
+  // epilogue
+  const int h0 = hg * kMmaRows + g, h1 = h0 + 8;
+  if (n_splits == 1) {
+    const float i0 = 1.0f / l0, i1 = 1.0f / l1;
+#pragma unroll
+    for (int nt = 0; nt < NTV; ++nt) {
+      const int col = (warp * NTV + nt) * 8 + 2 * t;
+      if (h0 < H) {
+        __nv_bfloat16* o = out + (size_t)h0 * out_hs + (size_t)row * out_ts;
+        if (col < rank) o[col] = __float2bfloat16_rn(acc[nt][0] * i0);
+        if (col + 1 < rank) o[col + 1] = __float2bfloat16_rn(acc[nt][1] * i0);
+      }
+      if (h1 < H) {
+        __nv_bfloat16* o = out + (size_t)h1 * out_hs + (size_t)row * out_ts;
+        if (col < rank) o[col] = __float2bfloat16_rn(acc[nt][2] * i1);
+        if (col + 1 < rank) o[col + 1] = __float2bfloat16_rn(acc[nt][3] * i1);
+      }
+    }
+  } else {
+#pragma unroll
+    for (int nt = 0; nt < NTV; ++nt) {
+      const int col = (warp * NTV + nt) * 8 + 2 * t;
+      if (h0 < H) {
+        float* o = o_part + (((size_t)z * rows + row) * H + h0) * rank;
+        if (col < rank) o[col] = acc[nt][0];
+        if (col + 1 < rank) o[col + 1] = acc[nt][1];
+      }
+      if (h1 < H) {
+        float* o = o_part + (((size_t)z * rows + row) * H + h1) * rank;
+        if (col < rank) o[col] = acc[nt][2];
+        if (col + 1 < rank) o[col + 1] = acc[nt][3];
+      }
+    }
+    if (warp == 0 && t == 0) {
+      if (h0 < H) {
+        float* ml = ml_part + (((size_t)z * rows + row) * H + h0) * 2;
+        ml[0] = m0; ml[1] = l0;
+      }
+      if (h1 < H) {
+        float* ml = ml_part + (((size_t)z * rows + row) * H + h1) * 2;
+        ml[0] = m1; ml[1] = l1;
+      }
+    }
+  }
+}
+
+__global__ void latent_combine_kernel(__nv_bfloat16* __restrict__ out, int64_t out_hs, int64_t out_ts,
+                                      const float* __restrict__ o_part, const float* __restrict__ ml_part,
+                                      int n_splits, int rows, int H, int rank) {
+  const int row = blockIdx.x, h = blockIdx.y;
+  float M = -INFINITY;
+  for (int z = 0; z < n_splits; ++z) M = fmaxf(M, ml_part[(((size_t)z * rows + row) * H + h) * 2]);
+  float L = 0.0f;
+  for (int z = 0; z < n_splits; ++z) {
+    const float* ml = ml_part + (((size_t)z * rows + row) * H + h) * 2;
+    if (ml[0] != -INFINITY) L += expf(ml[0] - M) * ml[1];
+  }
+  const float inv = 1.0f / L;
+  for (int c = threadIdx.x; c < rank; c += blockDim.x) {
+    float a = 0.0f;
+    for (int z = 0; z < n_splits; ++z) {
+      const size_t base = ((size_t)z * rows + row) * H + h;
+      const float mz = ml_part[base * 2];
+      if (mz != -INFINITY) a += expf(mz - M) * o_part[base * rank + c];
+    }
+    out[(size_t)h * out_hs + (size_t)row * out_ts + c] = __float2bfloat16_rn(a * inv);
+  }
+}
+
+template <typename QA, int NTV>
+int launch_latent_mma(void* out, int64_t out_hs, int64_t out_ts, float* o_part, float* ml_part, int n_splits,
+                      const void* qa, int64_t qa_hs, int64_t qa_ts, const void* q, int64_t ldq,
+                      const void* cache, int64_t ldc, const int* q_cu, const int* kv_cu, const int* tables,
+                      const int* blk_cu, const int* token_seq, int64_t rows, int H, int dim, int rd, int rank,
+                      int block_size, float scale, cudaStream_t st) {
+  const int DkP = (rank + rd + 31) / 32 * 32, ld = DkP + 8;
+  const size_t smem = ((size_t)(kMmaRows + kTileKeys) * ld + 16) * sizeof(__nv_bfloat16) + kMmaRows * 36 * sizeof(float);
+  auto kern = latent_attn_mma_kernel<QA, NTV>;
+  if (smem > 48 * 1024)
+    B200_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  dim3 grid((unsigned)rows, (unsigned)((H + kMmaRows - 1) / kMmaRows), (unsigned)n_splits);
+  kern<<<grid, 128, smem, st>>>(static_cast<__nv_bfloat16*>(out), out_hs, out_ts, o_part, ml_part, n_splits,
+                                static_cast<const QA*>(qa), qa_hs, qa_ts, static_cast<const __nv_bfloat16*>(q), ldq,
+                                static_cast<const __nv_bfloat16*>(cache), ldc, q_cu, kv_cu, tables, blk_cu,
+                                token_seq, (int)rows, H, dim, rd, rank, block_size, scale);
+  B200_LAUNCH_OK("latent_attn_mma_kernel");
+  if (n_splits > 1) {
+    latent_combine_kernel<<<dim3((unsigned)rows, (unsigned)H), 128, 0, st>>>(
+        static_cast<__nv_bfloat16*>(out), out_hs, out_ts, o_part, ml_part, n_splits, (int)rows, H, rank);
+    B200_LAUNCH_OK("latent_combine_kernel");
+  }
+  return B200_OK;
+}
+
+template <typename QA>
+int dispatch_mma(int rank, void* out, int64_t out_hs, int64_t out_ts, float* o_part, float* ml_part, int n_splits,
+                 const void* qa, int64_t qa_hs, int64_t qa_ts, const void* q, int64_t ldq, const void* cache,
+                 int64_t ldc, const int* q_cu, const int* kv_cu, const int* tables, const int* blk_cu,
+                 const int* token_seq, int64_t rows, int H, int dim, int rd, int block_size, float scale,
+                 cudaStream_t st) {
+#define LM_ARGS out, out_hs, out_ts, o_part, ml_part, n_splits, qa, qa_hs, qa_ts, q, ldq, cache, ldc, q_cu, kv_cu, \
+                tables, blk_cu, token_seq, rows, H, dim, rd, rank, block_size, scale, st
+  const int need = (rank + 31) / 32;   // 8-column tiles per warp (4 warps share the latent columns)
+  if (need <= 2) return launch_latent_mma<QA, 2>(LM_ARGS);
+  if (need <= 4) return launch_latent_mma<QA, 4>(LM_ARGS);
+  if (need <= 8) return launch_latent_mma<QA, 8>(LM_ARGS);
+  if (need <= 16) return launch_latent_mma<QA, 16>(LM_ARGS);
+#undef LM_ARGS
+  return set_error(B200_ERR_UNSUPPORTED, "latent_attn: latent rank %d > 512", rank);
+}
+
 }  // namespace
 }  // namespace b200
 
@@ -221,12 +502,18 @@ int b200_latent_prepare(void* q, int64_t ldq, const void* dkv, int64_t ld_dkv, v
   return B200_OK;
 }
 
+int64_t b200_latent_attn_workspace_bytes(int64_t rows, int64_t H, int64_t rank, int64_t n_splits) {
+  if (n_splits <= 1) return 0;
+  return n_splits * rows * H * (rank + 2) * (int64_t)sizeof(float);
+}
+
 int b200_latent_attn(void* out, int64_t out_head_stride, int64_t out_token_stride, const void* q_absorbed,
                      int64_t qa_head_stride, int64_t qa_token_stride, int qa_is_fp32, const void* q,
                      int64_t ldq, const void* cache, int64_t ldc, const int32_t* q_cu_lens,
                      const int32_t* kv_cu_lens, const int32_t* block_tables, const int32_t* cu_block_lens,
                      const int32_t* token_seq, int64_t rows, int64_t H, int64_t dim, int64_t rd,
-                     int64_t rank, int64_t block_size, float scale, int dtype, b200_stream_t stream) {
+                     int64_t rank, int64_t block_size, float scale, int n_splits, void* workspace,
+                     int64_t workspace_bytes, int dtype, b200_stream_t stream) {
   if (rows == 0) return B200_OK;
   B200_CHECK_ARG(out && q_absorbed && q && cache && q_cu_lens && kv_cu_lens && block_tables &&
                      cu_block_lens && token_seq,
@@ -240,6 +527,29 @@ int b200_latent_attn(void* out, int64_t out_head_stride, int64_t out_token_strid
                             qa_token_stride, q, ldq, cache, ldc, q_cu_lens, kv_cu_lens, block_tables,    \
                             cu_block_lens, token_seq, rows, (int)H, (int)dim, (int)rd, (int)block_size,   \
                             scale, st)
+  if (dtype == B200_BF16 && n_splits >= 1) {   // tensor-core form
+    B200_CHECK_ARG((rank + rd) % 8 == 0 && ldc % 8 == 0 && is_aligned(cache, 16),
+                   "latent_attn: the tensor-core form needs 16-byte aligned cache rows (rank + rot_dim and the row "
+                   "stride multiples of 8); pass n_splits = 0 for the CUDA-core form");
+    B200_CHECK_ARG(n_splits <= 65535, "latent_attn: too many splits");
+    float *o_part = nullptr, *ml_part = nullptr;
+    if (n_splits > 1) {
+      const int64_t need = b200_latent_attn_workspace_bytes(rows, H, rank, n_splits);
+      B200_CHECK_ARG(workspace && workspace_bytes >= need && is_aligned(workspace, 16),
+                     "latent_attn: workspace of %lld bytes required", (long long)need);
+      o_part = static_cast<float*>(workspace);
+      ml_part = o_part + (size_t)n_splits * rows * H * rank;
+    }
+    if (qa_is_fp32)
+      return dispatch_mma<float>((int)rank, out, out_head_stride, out_token_stride, o_part, ml_part, n_splits,
+                                 q_absorbed, qa_head_stride, qa_token_stride, q, ldq, cache, ldc, q_cu_lens,
+                                 kv_cu_lens, block_tables, cu_block_lens, token_seq, rows, (int)H, (int)dim,
+                                 (int)rd, (int)block_size, scale, st);
+    return dispatch_mma<__nv_bfloat16>((int)rank, out, out_head_stride, out_token_stride, o_part, ml_part,
+                                       n_splits, q_absorbed, qa_head_stride, qa_token_stride, q, ldq, cache, ldc,
+                                       q_cu_lens, kv_cu_lens, block_tables, cu_block_lens, token_seq, rows, (int)H,
+                                       (int)dim, (int)rd, (int)block_size, scale, st);
+  }
   switch (dtype) {
     case B200_BF16:
       if (qa_is_fp32) { LA_CALL(__nv_bfloat16, float); }

@@ -15,6 +15,7 @@ CPU tensors are rejected — there is no fallback path.
 from __future__ import annotations
 
 import ctypes as C
+import os
 from typing import NamedTuple, Dict, Optional, Tuple
 
 import torch
@@ -727,24 +728,41 @@ def latent_prepare(q: torch.Tensor, dkv: torch.Tensor, cache: torch.Tensor, c_no
                                           _stream()))
 
 
+def latent_attn_splits(rows: int, n_heads: int, kv_max: int, dtype: torch.dtype, width: int) -> int:
+    """How the keys of a row are cut over CTAs.  0: the CUDA-core kernel (fp32 models, rows that are not
+    16-byte multiples, B200_LATENT_IMPL=simt).  Otherwise the tensor-core kernel with enough key ranges to
+    give every SM about two CTAs when the step has few rows (decoding), one range when it has many."""
+    if dtype != torch.bfloat16 or width % 8 or os.environ.get("B200_LATENT_IMPL") == "simt":
+        return 0
+    ctas = rows * ((n_heads + 15) // 16)
+    want = -(-2 * 148 // max(ctas, 1))
+    return max(1, min(want, -(-kv_max // 128), 64))
+
+
 def latent_attn(q_absorbed: torch.Tensor, q: torch.Tensor, cache: torch.Tensor, q_cu: torch.Tensor,
                 kv_cu: torch.Tensor, block_tables: torch.Tensor, cu_block_lens: torch.Tensor,
                 token_seq: torch.Tensor, n_heads: int, dim: int, rot_dim: int, rank: int, block_size: int,
-                scale: float) -> torch.Tensor:
+                scale: float, kv_max: int = 0) -> torch.Tensor:
     """q_absorbed [H, rows, rank] (fp32 or q's dtype), q [rows, >= H * (dim + rot_dim)] with the rotary
-    parts already rotated; returns the attention-weighted latents [H, rows, rank] in q's dtype."""
+    parts already rotated; returns the attention-weighted latents [H, rows, rank] in q's dtype.
+    kv_max: the longest cached length of the step (a host number; it only steers the key split)."""
     _cuda(q_absorbed, q, cache)
     _check_i32(q_cu, kv_cu, block_tables, cu_block_lens, token_seq)
     rows = q.shape[0]
     assert q_absorbed.shape == (n_heads, rows, rank) and q_absorbed.stride(2) == 1
     assert q_absorbed.dtype in (torch.float32, q.dtype) and q.stride(1) == 1 and cache.dtype == q.dtype
     out = torch.empty((n_heads, rows, rank), dtype=q.dtype, device=q.device)
+    splits = latent_attn_splits(rows, n_heads, kv_max, q.dtype, rank + rot_dim) if cache.stride(0) % 8 == 0 else 0
+    ws, ws_bytes = None, 0
+    if splits > 1:
+        ws_bytes = int(_lib.load().b200_latent_attn_workspace_bytes(rows, n_heads, rank, splits))
+        ws = _workspace("latent_attn", q.device, ws_bytes)
     check(_lib.load().b200_latent_attn(_p(out), out.stride(0), out.stride(1), _p(q_absorbed),
                                        q_absorbed.stride(0), q_absorbed.stride(1),
                                        1 if q_absorbed.dtype == torch.float32 else 0, _p(q), q.stride(0),
                                        _p(cache), cache.stride(0), _p(q_cu), _p(kv_cu), _p(block_tables),
                                        _p(cu_block_lens), _p(token_seq), rows, n_heads, dim, rot_dim, rank,
-                                       block_size, scale, _dt(q), _stream()))
+                                       block_size, scale, splits, _p(ws), ws_bytes, _dt(q), _stream()))
     return out
 
 

@@ -677,7 +677,7 @@ class LatentAttention:
         self.H, self.dim, self.rd, self.vd, self.rank = n_heads, dim, rot_dim, vdim, rank
         self.scale, self.rot_mult, self.rot_dims, self.eps, self.dtype = scale, rot_mult, rot_dims, eps, dtype
         self.inv_freq = inv_freq.to(torch.float32).to(device).contiguous()
-        qw = H_dq = n_heads * (dim + rot_dim)
+        qw = n_heads * (dim + rot_dim)
         parts = [w["q"], w["dkv"]] + ([w["g"]] if "g" in w else [])
         self.has_gate = "g" in w
         self.in_proj = Linear(torch.cat(parts, dim=0))          # one GEMM for everything that reads h
@@ -686,7 +686,6 @@ class LatentAttention:
         self.uk = w["uk"].reshape(n_heads, dim, rank).contiguous()               # [H, dim, rank]
         self.uv_t = w["uv"].reshape(n_heads, vdim, rank).transpose(1, 2).contiguous()   # [H, rank, vdim]
         self.o_proj = Linear(w["o"])
-        del H_dq
 
     def forward(self, h: torch.Tensor, positions: torch.Tensor, cache: LatentKVCache,
                 params: InputParameters) -> torch.Tensor:
@@ -697,13 +696,10 @@ class LatentAttention:
         kernels.latent_prepare(q, dkv, cache.rows, self.c_norm, self.inv_freq, self.rot_mult, positions,
                                params.new_cache_slots, H, dim, rd, self.rot_dims, rank, self.eps)
         qu = q.view(T, H, dim + rd)[:, :, :dim].transpose(0, 1)                 # [H, T, dim] (strided view)
-        if self.dtype == torch.float32:
-            qa = torch.bmm(qu, self.uk)
-        else:   # keep the folded query in fp32: scores are formed in fp32 from it
-            qa = torch.bmm(qu.contiguous(), self.uk, out_dtype=torch.float32)
+        qa = torch.bmm(qu, self.uk)                                             # folded query [H, T, rank]
         lat = kernels.latent_attn(qa, q, cache.rows, params.q_cu_seq_lens, params.kv_cu_seq_lens,
                                   params.block_tables, params.cu_block_lens, params.token_seq, H, dim, rd, rank,
-                                  cache.block_size(), self.scale)
+                                  cache.block_size(), self.scale, params.kv_max_seq_len)
         o = torch.bmm(lat, self.uv_t)                                           # [H, T, vdim]
         o = kernels.heads_to_rows(o, proj[:, self.dkv_end:] if self.has_gate else None)
         return self.o_proj(o)
