@@ -541,6 +541,15 @@ B200_API int b200_grouped_gemm(void* C, int64_t ldc, const void* A, int64_t lda,
                                const float* pair_scale /*nullable*/, int64_t top, const void* weights,
                                const int32_t* offsets, int64_t n_rows, int64_t E, int64_t N, int64_t K, int dtype,
                                b200_stream_t stream);
+/* The same product for few rows per expert (decoding): the weights are streamed once per 8 rows of an expert. */
+B200_API int b200_grouped_gemv(void* C, int64_t ldc, const void* A, int64_t lda, const int32_t* sorted_pair /*nullable*/,
+                               const float* pair_scale /*nullable*/, int64_t top, const void* weights,
+                               const int32_t* offsets, int64_t n_rows, int64_t E, int64_t N, int64_t K, int dtype,
+                               b200_stream_t stream);
+/* xs[pos] = pair_scale[pair] * h[pair / top] in sorted order: the input of a library grouped GEMM. */
+B200_API int b200_moe_gather(void* xs, const void* h, int64_t ldh, const int32_t* sorted_pair,
+                             const float* pair_scale /*nullable*/, int64_t top, int64_t n_pairs, int64_t W, int dtype,
+                             b200_stream_t stream);
 B200_API int b200_moe_combine(void* out, const void* Y, int64_t ldy, const int32_t* pos_of_pair, int64_t rows,
                               int64_t W, int64_t top, int dtype, b200_stream_t stream);
 

@@ -113,6 +113,9 @@ SIGNATURES = {
     "b200_moe_plan": (_int, [_vp, _vp, _vp, _vp, _i64, _i64, _vp]),
     "b200_grouped_gemm": (_int, [_vp, _i64, _vp, _i64, _vp, _vp, _i64, _vp, _vp, _i64, _i64, _i64, _i64,
                                  _int, _vp]),
+    "b200_grouped_gemv": (_int, [_vp, _i64, _vp, _i64, _vp, _vp, _i64, _vp, _vp, _i64, _i64, _i64, _i64,
+                                 _int, _vp]),
+    "b200_moe_gather": (_int, [_vp, _vp, _i64, _vp, _vp, _i64, _i64, _i64, _int, _vp]),
     "b200_moe_combine": (_int, [_vp, _vp, _i64, _vp, _i64, _i64, _i64, _int, _vp]),
 }
 

@@ -160,6 +160,92 @@ grouped_gemm_kernel(T* __restrict__ C, int64_t ldc, const T* __restrict__ A, int
   }
 }
 
+
+// Few rows per expert (decoding): the weights are the traffic.  One CTA per (expert, 16 output columns):
+// the expert's rows, MB at a time, sit in shared memory; every warp streams two weight rows at a time with
+// 16-byte loads and keeps MB x 2 dot products per lane, reduced over the warp at the end.  Sums run in k
+// order per lane and then over lanes: a row's result does not depend on which rows share its pass.
+constexpr int GV_MB = 8, GV_WARPS = 8, GV_CPW = 2;
+
+template <typename T>
+__global__ void __launch_bounds__(GV_WARPS * 32)
+grouped_gemv_kernel(T* __restrict__ C, int64_t ldc, const T* __restrict__ A, int64_t lda,
+                    const int* __restrict__ sorted_pair, const float* __restrict__ pair_scale, int top,
+                    const T* __restrict__ Wst, const int* __restrict__ offsets, int N, int K) {
+  extern __shared__ __align__(16) unsigned char gv_smem[];
+  T* As = reinterpret_cast<T*>(gv_smem);                     // [GV_MB][K]
+  constexpr int VEC = 16 / sizeof(T);
+  const int e = blockIdx.y, lo = offsets[e], hi = offsets[e + 1];
+  if (lo >= hi) return;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n0 = (blockIdx.x * GV_WARPS + warp) * GV_CPW;
+  const T* Wm = Wst + (size_t)e * N * K;
+  for (int m0 = lo; m0 < hi; m0 += GV_MB) {
+    __syncthreads();
+    for (int m = 0; m < GV_MB; ++m) {
+      const int pos = m0 + m;
+      int src = -1;
+      float sc = 1.0f;
+      if (pos < hi) {
+        if (sorted_pair) {
+          const int p = sorted_pair[pos];
+          src = p / top;
+          sc = pair_scale ? pair_scale[p] : 1.0f;
+        } else {
+          src = pos;
+        }
+      }
+      for (int k = threadIdx.x; k < K; k += GV_WARPS * 32)
+        As[m * K + k] = src >= 0 ? Num<T>::from_f(Num<T>::to_f(A[(size_t)src * lda + k]) * sc) : Num<T>::from_f(0.0f);
+    }
+    __syncthreads();
+    if (n0 < N) {
+      float acc[GV_CPW][GV_MB];
+#pragma unroll
+      for (int c = 0; c < GV_CPW; ++c)
+#pragma unroll
+        for (int m = 0; m < GV_MB; ++m) acc[c][m] = 0.0f;
+      for (int k = lane * VEC; k < K; k += 32 * VEC) {
+        T w[GV_CPW][VEC];
+#pragma unroll
+        for (int c = 0; c < GV_CPW; ++c) {
+          const int n = n0 + c < N ? n0 + c : N - 1;
+          *reinterpret_cast<uint4*>(w[c]) = *reinterpret_cast<const uint4*>(Wm + (size_t)n * K + k);
+        }
+#pragma unroll
+        for (int m = 0; m < GV_MB; ++m) {
+          T a[VEC];
+          *reinterpret_cast<uint4*>(a) = *reinterpret_cast<const uint4*>(As + m * K + k);
+#pragma unroll
+          for (int v = 0; v < VEC; ++v) {
+            const float av = Num<T>::to_f(a[v]);
+#pragma unroll
+            for (int c = 0; c < GV_CPW; ++c) acc[c][m] += av * Num<T>::to_f(w[c][v]);
+          }
+        }
+      }
+#pragma unroll
+      for (int c = 0; c < GV_CPW; ++c)
+#pragma unroll
+        for (int m = 0; m < GV_MB; ++m) {
+          const float v = warp_sum(acc[c][m]);
+          if (lane == 0 && n0 + c < N && m0 + m < hi) C[(size_t)(m0 + m) * ldc + n0 + c] = Num<T>::from_f(v);
+        }
+    }
+  }
+}
+
+// xs[pos] = pair_scale[pair] * h[pair / top]: the experts' input rows in sorted order (for a library grouped GEMM)
+template <typename T>
+__global__ void moe_gather_kernel(T* __restrict__ xs, const T* __restrict__ h, int64_t ldh,
+                                  const int* __restrict__ sorted_pair, const float* __restrict__ pair_scale,
+                                  int top, int W) {
+  const int pos = blockIdx.x, p = sorted_pair[pos];
+  const float sc = pair_scale ? pair_scale[p] : 1.0f;
+  const T* src = h + (size_t)(p / top) * ldh;
+  for (int i = threadIdx.x; i < W; i += blockDim.x) xs[(size_t)pos * W + i] = Num<T>::from_f(Num<T>::to_f(src[i]) * sc);
+}
+
 template <typename T>
 __global__ void moe_combine_kernel(T* __restrict__ out, const T* __restrict__ Y, int64_t ldy,
                                    const int* __restrict__ pos_of_pair, int W, int top) {
@@ -227,6 +313,50 @@ int b200_grouped_gemm(void* C, int64_t ldc, const void* A, int64_t lda, const in
                           static_cast<T*>(C), ldc, static_cast<const T*>(A), lda, sorted_pair, pair_scale,
                           (int)top, static_cast<const T*>(weights), offsets, (int)E, (int)N, (int)K)));
   B200_LAUNCH_OK("grouped_gemm_kernel");
+  return B200_OK;
+}
+
+int b200_grouped_gemv(void* C, int64_t ldc, const void* A, int64_t lda, const int32_t* sorted_pair,
+                      const float* pair_scale, int64_t top, const void* weights, const int32_t* offsets,
+                      int64_t n_rows, int64_t E, int64_t N, int64_t K, int dtype, b200_stream_t stream) {
+  if (n_rows == 0) return B200_OK;
+  B200_CHECK_ARG(C && A && weights && offsets, "grouped_gemv: null pointer");
+  const int es = dtype == B200_FP32 ? 4 : 2;
+  B200_CHECK_ARG(E >= 1 && E <= 65535 && N > 0 && K > 0 && ldc >= N && lda >= K && top >= 1 && (K * es) % 16 == 0 &&
+                     is_aligned(weights, 16) && (int64_t)GV_MB * K * es <= 200 * 1024,
+                 "grouped_gemv: K rows of 16-byte multiples that fit in shared memory %d at a time", GV_MB);
+  const size_t smem = (size_t)GV_MB * K * es;
+  dim3 grid((unsigned)((N + GV_WARPS * GV_CPW - 1) / (GV_WARPS * GV_CPW)), (unsigned)E);
+  auto st = static_cast<cudaStream_t>(stream);
+#define GV_LAUNCH(T)                                                                                      \
+  {                                                                                                       \
+    auto kern = grouped_gemv_kernel<T>;                                                                   \
+    if (smem > 48 * 1024)                                                                                 \
+      B200_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));   \
+    kern<<<grid, GV_WARPS * 32, smem, st>>>(static_cast<T*>(C), ldc, static_cast<const T*>(A), lda,       \
+                                            sorted_pair, pair_scale, (int)top, static_cast<const T*>(weights), \
+                                            offsets, (int)N, (int)K);                                     \
+  }
+  switch (dtype) {
+    case B200_BF16: GV_LAUNCH(__nv_bfloat16); break;
+    case B200_FP16: GV_LAUNCH(__half); break;
+    case B200_FP32: GV_LAUNCH(float); break;
+    default: return set_error(B200_ERR_INVALID_ARG, "bad dtype %d", dtype);
+  }
+#undef GV_LAUNCH
+  B200_LAUNCH_OK("grouped_gemv_kernel");
+  return B200_OK;
+}
+
+int b200_moe_gather(void* xs, const void* h, int64_t ldh, const int32_t* sorted_pair, const float* pair_scale,
+                    int64_t top, int64_t n_pairs, int64_t W, int dtype, b200_stream_t stream) {
+  if (n_pairs == 0) return B200_OK;
+  B200_CHECK_ARG(xs && h && sorted_pair, "moe_gather: null pointer");
+  B200_CHECK_ARG(n_pairs > 0 && W > 0 && ldh >= W && top >= 1, "moe_gather: bad shape");
+  auto st = static_cast<cudaStream_t>(stream);
+  MOE_DISPATCH(dtype, (moe_gather_kernel<T><<<(unsigned)n_pairs, 256, 0, st>>>(
+                          static_cast<T*>(xs), static_cast<const T*>(h), ldh, sorted_pair, pair_scale, (int)top, (int)W)));
+  B200_LAUNCH_OK("moe_gather_kernel");
   return B200_OK;
 }
 

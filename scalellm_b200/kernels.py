@@ -840,9 +840,27 @@ def grouped_gemm(a: torch.Tensor, weights: torch.Tensor, offsets: torch.Tensor, 
         _check_i32(sorted_pair)
         _f32(pair_scale)
     out = torch.empty((n_rows, N), dtype=a.dtype, device=a.device)
+    es = a.element_size()
+    if n_rows <= _GEMV_ROWS and (K * es) % 16 == 0 and 8 * K * es <= 200 * 1024:
+        # decoding: a few rows per expert, the weights are the traffic
+        check(_lib.load().b200_grouped_gemv(_p(out), N, _p(a), a.stride(0), _p(sorted_pair), _p(pair_scale), top,
+                                            _p(weights), _p(offsets), n_rows, E, N, K, _dt(a), _stream()))
+        return out
+    if (a.dtype == torch.bfloat16 and K % 8 == 0 and N % 8 == 0 and os.environ.get("B200_MOE_IMPL") != "tile"):
+        # prompt-sized: the library's grouped GEMM over the sorted rows (the group ends are offsets[1:])
+        if sorted_pair is not None:
+            xs = torch.empty((n_rows, K), dtype=a.dtype, device=a.device)
+            check(_lib.load().b200_moe_gather(_p(xs), _p(a), a.stride(0), _p(sorted_pair), _p(pair_scale), top,
+                                              n_rows, K, _dt(a), _stream()))
+        else:
+            xs = a if a.is_contiguous() else a.contiguous()
+        return torch.nn.functional.grouped_mm(xs, weights.transpose(1, 2), offs=offsets[1:])
     check(_lib.load().b200_grouped_gemm(_p(out), N, _p(a), a.stride(0), _p(sorted_pair), _p(pair_scale), top,
                                         _p(weights), _p(offsets), n_rows, E, N, K, _dt(a), _stream()))
     return out
+
+
+_GEMV_ROWS = 256   # at most this many (token, choice) rows: the weight-streaming kernel
 
 
 def moe_combine(y: torch.Tensor, pos_of_pair: torch.Tensor, rows: int, top: int) -> torch.Tensor:
