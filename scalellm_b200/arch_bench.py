@@ -100,7 +100,7 @@ def _run_model(config: dict, batch: int, seqlen: int, warmup: int, steps: int, k
     model.init_random(seed)
     bs = 16
     eng = Engine(model, max_tokens=batch * (seqlen + 64 + bs), block_size=bs, max_seqs=batch,
-                 max_step_tokens=batch * seqlen)
+                 max_step_tokens=batch * seqlen, use_graphs=True)
     g = torch.Generator().manual_seed(seed)
     V = config.get("vocab", config.get("vocab_size"))
     prompts = [[int(x) for x in torch.randint(0, V, (seqlen,), generator=g)] for _ in range(batch)]
@@ -133,6 +133,7 @@ def _run_model(config: dict, batch: int, seqlen: int, warmup: int, steps: int, k
     timer.wrap(torch.nn.functional, ["linear"], lambda n: "linear (dense GEMMs)")
     timer.wrap(torch, ["bmm"], lambda n: "bmm (per-head key / value maps)")
     try:
+        eng.use_graphs = False          # per-kernel times come from eager steps
         decode()
         res["decode"]["kernels_ms"] = timer.totals_ms()
         prefill_once()

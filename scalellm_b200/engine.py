@@ -142,8 +142,12 @@ class Scheduler:
 
 class Engine:
     def __init__(self, model, max_tokens: int, block_size: int = 16, max_seqs: int = 4,
-                 max_step_tokens: Optional[int] = None, pool_seed: int = 2):
-        """max_tokens: tokens the cache pool holds at any time, each sequence rounded up to whole blocks."""
+                 max_step_tokens: Optional[int] = None, pool_seed: int = 2, use_graphs: bool = False):
+        """max_tokens: tokens the cache pool holds at any time, each sequence rounded up to whole blocks.
+        use_graphs: steps in which every sequence brings one token (decoding) replay a CUDA graph, captured
+        per batch size and power-of-two bucket of the longest cached length once such a step has run twice
+        eagerly (the eager runs create the workspaces and library handles a capture must not create; a
+        warm-up run of its own would advance the recurrent state twice)."""
         self.model, self.max_seqs = model, max_seqs
         self.device = model.device
         n_blocks = -(-max_tokens // block_size)
@@ -154,6 +158,9 @@ class Engine:
         self.bufs = StepBuffers(self.device, self.max_step_tokens, max_seqs, n_blocks + max_seqs)
         self.seqs: Dict[str, Sequence_] = {}
         self.sampler = Sampler(self.device)
+        self.use_graphs = use_graphs and self.device.type == "cuda"
+        self._graphs: Dict[Tuple[int, int], Tuple[torch.cuda.CUDAGraph, torch.Tensor]] = {}
+        self._seen: Dict[Tuple[int, int], int] = {}
 
     # ---------------------------------------------------------------- sequences
     def open(self, rid: str) -> Sequence_:
@@ -191,12 +198,37 @@ class Engine:
             raise ValueError(f"{row0} tokens in one step; the engine was made for {self.max_step_tokens}")
         hb = build_step_batch(self.pool, [s.seq for s in seqs], [e.tokens for e in entries],
                               [s.n_cached for s in seqs], [s.slot for s in seqs] if self.slots else None)
-        tokens, positions, params = self.bufs.upload(hb)
         idx = torch.tensor(want, dtype=torch.int32).to(self.device, non_blocking=True)
-        logits = self.model.forward(tokens, positions, params, last_token_idxes=idx)
+        if self.use_graphs and row0 == len(entries):
+            logits = self._decode_step(hb, idx, want)
+        else:
+            tokens, positions, params = self.bufs.upload(hb)
+            logits = self.model.forward(tokens, positions, params, last_token_idxes=idx)
         for e, s in zip(entries, seqs):
             s.n_cached += len(e.tokens)
         return logits
+
+    def _decode_step(self, hb, idx: torch.Tensor, want: List[int]) -> torch.Tensor:
+        """One token per sequence: replay (or, the third time round, capture) the step's CUDA graph."""
+        B = len(hb.q_cu_lens) - 1
+        bucket = 256
+        while bucket < hb.kv_max:
+            bucket *= 2
+        key = (B, bucket)
+        hb.kv_max = bucket            # an upper bound: it sizes work partitions, the lengths come from the device
+        tokens, positions, params = self.bufs.upload(hb)
+        if key not in self._graphs:
+            self._seen[key] = self._seen.get(key, 0) + 1
+            if self._seen[key] <= 2:
+                return self.model.forward(tokens, positions, params, last_token_idxes=idx)
+            torch.cuda.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                out = self.model.forward(tokens, positions, params)
+            self._graphs[key] = (graph, out)
+        graph, out = self._graphs[key]
+        graph.replay()
+        return out if want == list(range(B)) else out.index_select(0, idx)
 
     # ---------------------------------------------------------------- generation
     def generate(self, prompts: Sequence[Sequence[int]], sampling: Optional[Sequence[SamplingParams]] = None,

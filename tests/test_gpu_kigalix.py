@@ -24,9 +24,9 @@ def build(cfg, dtype, seed=0, max_seqs=4):
     return model, ok.Kigalix(cfg, w)
 
 
-def engine_for(model, max_tokens=512, block_size=4, max_seqs=4):
+def engine_for(model, max_tokens=512, block_size=4, max_seqs=4, use_graphs=False):
     from scalellm_b200.engine import Engine
-    return Engine(model, max_tokens, block_size=block_size, max_seqs=max_seqs)
+    return Engine(model, max_tokens, block_size=block_size, max_seqs=max_seqs, use_graphs=use_graphs)
 
 
 def oracle_logits(oracle, tokens):
@@ -277,6 +277,30 @@ def test_long_decoding_over_many_blocks():
     tokens = toks(140, cfg["vocab"], 9)
     got = run_schedule(engine_for(model, block_size=2), tokens, [3])      # 137 single-token steps
     assert kc.logits_error(got, oracle_logits(oracle, tokens)) < TOL[torch.float32]
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_decoding_by_graph_replay(dtype):
+    """Single-token steps replay a captured graph from the third step on; two sequences decode side by side,
+    and a third batch size (one sequence left) gets a graph of its own."""
+    from scalellm_b200.engine import StepEntry
+    cfg = kc.CONFIGS["mix"]
+    model, oracle = build(cfg, dtype, seed=8)
+    a, b = toks(48, cfg["vocab"], 21), toks(30, cfg["vocab"], 22)
+    ref_a, ref_b = oracle_logits(oracle, a), oracle_logits(oracle, b)
+    eng = engine_for(model, block_size=4, use_graphs=True)
+    out = eng.step([StepEntry("a", a[:20], list(range(20))), StepEntry("b", b[:9], list(range(9)))]).float().cpu()
+    got_a, got_b = [out[:20]], [out[20:]]
+    for i in range(21):                                   # b ends first
+        out = eng.step([StepEntry("b", [b[9 + i]], [0]), StepEntry("a", [a[20 + i]], [0])]).float().cpu()
+        got_b.append(out[:1])
+        got_a.append(out[1:])
+    eng.finish("b")
+    for i in range(41, 48):
+        got_a.append(eng.step([StepEntry("a", [a[i]], [0])]).float().cpu())
+    assert len(eng._graphs) == 2
+    assert kc.logits_error(torch.cat(got_a), ref_a) < TOL[dtype]
+    assert kc.logits_error(torch.cat(got_b), ref_b) < TOL[dtype]
 
 
 def test_the_first_tokens_of_a_sequence():
