@@ -128,6 +128,146 @@ __global__ void gated_hc_update_kernel(float* __restrict__ X, const T* __restric
   }
 }
 
+
+// ---- four columns per thread (W % 4 == 0): the same arithmetic with 16-byte accesses to the fp32 streams
+template <typename T>
+__device__ __forceinline__ void load4(const T* p, float (&v)[4]) {
+#pragma unroll
+  for (int i = 0; i < 4; ++i) v[i] = Num<T>::to_f(p[i]);
+}
+template <>
+__device__ __forceinline__ void load4<__nv_bfloat16>(const __nv_bfloat16* p, float (&v)[4]) {
+  const uint2 u = *reinterpret_cast<const uint2*>(p);
+  const float2 a = Num<__nv_bfloat16>::unpack(u.x), b = Num<__nv_bfloat16>::unpack(u.y);
+  v[0] = a.x; v[1] = a.y; v[2] = b.x; v[3] = b.y;
+}
+template <>
+__device__ __forceinline__ void load4<float>(const float* p, float (&v)[4]) {
+  const float4 u = *reinterpret_cast<const float4*>(p);
+  v[0] = u.x; v[1] = u.y; v[2] = u.z; v[3] = u.w;
+}
+template <typename T>
+__device__ __forceinline__ void store4(T* p, const float (&v)[4]) {
+#pragma unroll
+  for (int i = 0; i < 4; ++i) p[i] = Num<T>::from_f(v[i]);
+}
+template <>
+__device__ __forceinline__ void store4<__nv_bfloat16>(__nv_bfloat16* p, const float (&v)[4]) {
+  uint2 u;
+  u.x = Num<__nv_bfloat16>::pack(v[0], v[1]);
+  u.y = Num<__nv_bfloat16>::pack(v[2], v[3]);
+  *reinterpret_cast<uint2*>(p) = u;
+}
+template <>
+__device__ __forceinline__ void store4<float>(float* p, const float (&v)[4]) {
+  *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kRowThreads)
+hc_norm_vec_kernel(T* __restrict__ out, float* __restrict__ out32, const float* __restrict__ X,
+                   const float* __restrict__ a, const float* __restrict__ w, int W, int S, float eps,
+                   float offset) {
+  extern __shared__ __align__(16) float u_s[];
+  __shared__ float red[32];
+  const int row = blockIdx.x;
+  const float* x = X + (size_t)row * S * W;
+  float coef[kMaxStreams];
+#pragma unroll
+  for (int s = 0; s < kMaxStreams; ++s) coef[s] = (s < S) ? (a ? a[s] : 1.0f) : 0.0f;
+  float ss = 0.0f;
+  for (int i = threadIdx.x * 4; i < W; i += kRowThreads * 4) {
+    float u[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+    for (int s = 0; s < kMaxStreams; ++s) {
+      if (s < S) {
+        const float4 v = *reinterpret_cast<const float4*>(x + (size_t)s * W + i);
+        u[0] += coef[s] * v.x; u[1] += coef[s] * v.y; u[2] += coef[s] * v.z; u[3] += coef[s] * v.w;
+      }
+    }
+    *reinterpret_cast<float4*>(u_s + i) = make_float4(u[0], u[1], u[2], u[3]);
+    ss += u[0] * u[0] + u[1] * u[1] + u[2] * u[2] + u[3] * u[3];
+  }
+  ss = block_sum<kRowThreads>(ss, red);
+  const float r = rsqrtf(ss / (float)W + eps);
+  for (int i = threadIdx.x * 4; i < W; i += kRowThreads * 4) {
+    const float4 u = *reinterpret_cast<const float4*>(u_s + i);
+    const float4 ww = *reinterpret_cast<const float4*>(w + i);
+    const float n[4] = {u.x * r * (offset + ww.x), u.y * r * (offset + ww.y), u.z * r * (offset + ww.z),
+                        u.w * r * (offset + ww.w)};
+    store4<T>(out + (size_t)row * W + i, n);
+    if (out32) store4<float>(out32 + (size_t)row * W + i, n);
+  }
+}
+
+// grid (rows, column chunks of 512)
+template <typename T>
+__global__ void __launch_bounds__(128)
+token_shift_vec_kernel(T* __restrict__ out, const float* __restrict__ n32, const float* __restrict__ mu,
+                       float* __restrict__ state, const int* __restrict__ q_cu,
+                       const int* __restrict__ positions, const int* __restrict__ token_seq,
+                       const int* __restrict__ state_slots, int W) {
+  const int row = blockIdx.x, i = (blockIdx.y * 128 + threadIdx.x) * 4;
+  if (i >= W) return;
+  const int seq = token_seq[row];
+  const int first = q_cu[seq], last = q_cu[seq + 1] - 1;
+  float n[4], p[4], m[4];
+  load4<float>(n32 + (size_t)row * W + i, n);
+  load4<float>(mu + i, m);
+  if (row != first) {
+    load4<float>(n32 + (size_t)(row - 1) * W + i, p);
+  } else {
+    float* slot = state + (size_t)state_slots[seq] * W + i;
+    if (positions[row] == 0) { p[0] = p[1] = p[2] = p[3] = 0.0f; } else { load4<float>(slot, p); }
+    float tail[4];
+    load4<float>(n32 + (size_t)last * W + i, tail);
+    store4<float>(slot, tail);
+  }
+  const float o[4] = {n[0] + (p[0] - n[0]) * m[0], n[1] + (p[1] - n[1]) * m[1], n[2] + (p[2] - n[2]) * m[2],
+                      n[3] + (p[3] - n[3]) * m[3]};
+  store4<T>(out + (size_t)row * W + i, o);
+}
+
+// grid (rows, column chunks of 512)
+template <typename T>
+__global__ void __launch_bounds__(128)
+gated_hc_update_vec_kernel(float* __restrict__ X, const T* __restrict__ y, const T* __restrict__ gate,
+                           const float* __restrict__ gate_bias, const float* __restrict__ mix,
+                           const float* __restrict__ outc, int W, int S, int64_t ldy, int64_t ldg) {
+  const int row = blockIdx.x, i = (blockIdx.y * 128 + threadIdx.x) * 4;
+  if (i >= W) return;
+  float* x = X + (size_t)row * S * W + i;
+  float v[4];
+  load4<T>(y + (size_t)row * ldy + i, v);
+  if (gate) {
+    float z[4], b[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+    load4<T>(gate + (size_t)row * ldg + i, z);
+    if (gate_bias) load4<float>(gate_bias + i, b);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) v[k] *= 1.0f / (1.0f + expf(-(z[k] + b[k])));
+  }
+  float old[kMaxStreams][4];
+#pragma unroll
+  for (int s = 0; s < kMaxStreams; ++s)
+    if (s < S) load4<float>(x + (size_t)s * W, old[s]);
+#pragma unroll
+  for (int t = 0; t < kMaxStreams; ++t) {
+    if (t < S) {
+      const float bt = outc ? outc[t] : 1.0f;
+      float acc[4] = {bt * v[0], bt * v[1], bt * v[2], bt * v[3]};
+#pragma unroll
+      for (int s = 0; s < kMaxStreams; ++s) {
+        if (s < S) {
+          const float m = mix ? mix[s * S + t] : (s == t ? 1.0f : 0.0f);
+#pragma unroll
+          for (int k = 0; k < 4; ++k) acc[k] += m * old[s][k];
+        }
+      }
+      store4<float>(x + (size_t)t * W, acc);
+    }
+  }
+}
+
 // out = act(in[:, :n]) * in[:, n:2n]; act 0 = SiLU, 1 = GELU (tanh form, tanhf), one rounding
 template <typename T>
 __global__ void gated_act_kernel(T* __restrict__ out, const T* __restrict__ in, int64_t rows, int n,
@@ -206,6 +346,12 @@ int b200_hc_norm(void* out, float* out32, const float* X, const float* collapse,
   B200_CHECK_ARG(out && X && weight, "hc_norm: null pointer");
   B200_CHECK_ARG(rows > 0 && W > 0 && W <= 12000 && S >= 1 && S <= kMaxStreams, "hc_norm: bad shape");
   auto st = static_cast<cudaStream_t>(stream);
+  if (W % 4 == 0 && is_aligned(out, 16) && is_aligned(X, 16) && is_aligned(weight, 16) && (!out32 || is_aligned(out32, 16))) {
+    HYPER_DISPATCH(dtype, (hc_norm_vec_kernel<T><<<(unsigned)rows, kRowThreads, W * sizeof(float), st>>>(
+                              static_cast<T*>(out), out32, X, collapse, weight, (int)W, (int)S, eps, offset)));
+    B200_LAUNCH_OK("hc_norm_vec_kernel");
+    return B200_OK;
+  }
   HYPER_DISPATCH(dtype, (hc_norm_kernel<T><<<(unsigned)rows, kRowThreads, W * sizeof(float), st>>>(
                             static_cast<T*>(out), out32, X, collapse, weight, (int)W, (int)S, eps, offset)));
   B200_LAUNCH_OK("hc_norm_kernel");
@@ -220,6 +366,13 @@ int b200_token_shift(void* out, const float* n32, const float* mu, float* state,
                  "token_shift: null pointer");
   B200_CHECK_ARG(rows > 0 && W > 0, "token_shift: bad shape");
   auto st = static_cast<cudaStream_t>(stream);
+  if (W % 4 == 0 && is_aligned(out, 16) && is_aligned(n32, 16) && is_aligned(mu, 16) && is_aligned(state, 16)) {
+    dim3 grid((unsigned)rows, (unsigned)((W + 511) / 512));
+    HYPER_DISPATCH(dtype, (token_shift_vec_kernel<T><<<grid, 128, 0, st>>>(
+                              static_cast<T*>(out), n32, mu, state, q_cu, positions, token_seq, state_slots, (int)W)));
+    B200_LAUNCH_OK("token_shift_vec_kernel");
+    return B200_OK;
+  }
   HYPER_DISPATCH(dtype, (token_shift_kernel<T><<<(unsigned)rows, 128, 0, st>>>(
                             static_cast<T*>(out), n32, mu, state, q_cu, positions, token_seq,
                             state_slots, (int)W)));
@@ -235,6 +388,16 @@ int b200_gated_hc_update(float* X, const void* y, int64_t ldy, const void* gate,
   B200_CHECK_ARG(rows > 0 && W > 0 && S >= 1 && S <= kMaxStreams && ldy >= W && (!gate || ldg >= W),
                  "gated_hc_update: bad shape");
   auto st = static_cast<cudaStream_t>(stream);
+  const int esz = dtype == B200_FP32 ? 4 : 2;
+  if (W % 4 == 0 && is_aligned(X, 16) && is_aligned(y, 4 * esz) && (ldy * esz) % (4 * esz) == 0 &&
+      (!gate || (is_aligned(gate, 4 * esz) && (ldg * esz) % (4 * esz) == 0)) && (!gate_bias || is_aligned(gate_bias, 16))) {
+    dim3 grid((unsigned)rows, (unsigned)((W + 511) / 512));
+    HYPER_DISPATCH(dtype, (gated_hc_update_vec_kernel<T><<<grid, 128, 0, st>>>(
+                              X, static_cast<const T*>(y), static_cast<const T*>(gate), gate_bias, mix, outc, (int)W,
+                              (int)S, ldy, ldg)));
+    B200_LAUNCH_OK("gated_hc_update_vec_kernel");
+    return B200_OK;
+  }
   HYPER_DISPATCH(dtype, (gated_hc_update_kernel<T><<<(unsigned)rows, 128, 0, st>>>(
                             X, static_cast<const T*>(y), static_cast<const T*>(gate), gate_bias, mix,
                             outc, (int)W, (int)S, ldy, ldg)));

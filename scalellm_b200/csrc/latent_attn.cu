@@ -229,8 +229,8 @@ latent_attn_mma_kernel(__nv_bfloat16* __restrict__ out, int64_t out_hs, int64_t 
   extern __shared__ __align__(16) unsigned char smem_raw[];
   const int Dk = rank + rd, DkP = (Dk + 31) / 32 * 32, ld = DkP + 8;
   __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(smem_raw);   // [16][ld]
-  __nv_bfloat16* Ks = Qs + kMmaRows * ld;                           // [32][ld] + 16 slack
-  float* Ss = reinterpret_cast<float*>(Ks + kTileKeys * ld + 16);   // [16][36]
+  __nv_bfloat16* Kbuf = Qs + kMmaRows * ld;                         // 2 x [32][ld], + 16 slack
+  float* Ss = reinterpret_cast<float*>(Kbuf + 2 * kTileKeys * ld + 16);   // [16][36]
   constexpr int lds = 36;
   const int row = blockIdx.x, hg = blockIdx.y, z = blockIdx.z;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
@@ -239,14 +239,18 @@ latent_attn_mma_kernel(__nv_bfloat16* __restrict__ out, int64_t out_hs, int64_t 
   const int pos = kv_len - q_len + (row - q_cu[seq]);
   const int* table = tables + blk_cu[seq];
   // stage Q: row r of the tile is head hg * 16 + r of this token: [folded query (rank) | rotary part (rd) | 0]
-  for (int idx = tid; idx < kMmaRows * ld; idx += 128) {
-    const int r = idx / ld, d = idx - r * ld, h = hg * kMmaRows + r;
-    float v = 0.0f;
-    if (h < H) {
-      if (d < rank) v = Num<QA>::to_f(qa[(size_t)h * qa_hs + (size_t)row * qa_ts + d]);
-      else if (d < Dk) v = __bfloat162float(q[(size_t)row * ldq + (size_t)h * (dim + rd) + dim + (d - rank)]);
+  for (int r = warp; r < kMmaRows; r += 4) {
+    const int h = hg * kMmaRows + r;
+    const bool live = h < H;
+    const QA* a = qa + (size_t)(live ? h : 0) * qa_hs + (size_t)row * qa_ts;
+    const __nv_bfloat16* qr = q + (size_t)row * ldq + (size_t)(live ? h : 0) * (dim + rd) + dim - rank;
+#pragma unroll 4
+    for (int d = lane; d < ld; d += 32) {
+      float v = 0.0f;
+      if (live && d < rank) v = Num<QA>::to_f(a[d]);
+      else if (live && d < Dk) v = __bfloat162float(qr[d]);
+      Qs[r * ld + d] = __float2bfloat16_rn(v);
     }
-    Qs[idx] = __float2bfloat16_rn(v);
   }
   const int tiles_total = pos / kTileKeys + 1;
   const int tps = (tiles_total + n_splits - 1) / n_splits;
@@ -257,29 +261,49 @@ latent_attn_mma_kernel(__nv_bfloat16* __restrict__ out, int64_t out_hs, int64_t 
   float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.0f, l1 = 0.0f;   // rows g and g + 8
   const int chunks = ld / 8;                                     // 16-byte chunks of a staged row
   const int rank8 = (rank + 7) / 8 * 8;
-  for (int tile = tile0; tile < tile1; ++tile) {
+  // the tile's rows arrive by 16-byte asynchronous copies into one of two buffers: tile i + 1 is in flight
+  // while tile i is used.  Rows beyond the last visible key and the padding chunks are zero-filled (size 0).
+  auto fetch = [&](int tile, __nv_bfloat16* Kd) {
     const int j0 = tile * kTileKeys;
-    __syncthreads();
     for (int jj = warp; jj < kTileKeys; jj += 4) {
       const int key = j0 + jj;
-      uint4* dst = reinterpret_cast<uint4*>(Ks + jj * ld);
-      if (key <= pos) {
-        const uint4* src = reinterpret_cast<const uint4*>(cache + ((size_t)table[key / block_size] + key % block_size) * ldc);
-        for (int c = lane; c < chunks; c += 32) dst[c] = (c * 8 < Dk) ? src[c] : make_uint4(0, 0, 0, 0);
-      } else {
-        for (int c = lane; c < chunks; c += 32) dst[c] = make_uint4(0, 0, 0, 0);
+      const bool vis = key <= pos;
+      const __nv_bfloat16* src = cache + (vis ? ((size_t)table[key / block_size] + key % block_size) * ldc : 0);
+      for (int c = lane; c < chunks; c += 32) {
+        const bool real = vis && c * 8 < Dk;
+        const uint32_t dst = smem_u32(Kd + jj * ld + c * 8);
+        const int nbytes = real ? 16 : 0;
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(real ? src + c * 8 : cache), "r"(nbytes) : "memory");
       }
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+  if (tile0 < tile1) fetch(tile0, Kbuf);
+  for (int tile = tile0; tile < tile1; ++tile) {
+    const int j0 = tile * kTileKeys;
+    __nv_bfloat16* Ks = Kbuf + ((tile - tile0) & 1) * kTileKeys * ld;
+    if (tile + 1 < tile1) {
+      fetch(tile + 1, Kbuf + ((tile + 1 - tile0) & 1) * kTileKeys * ld);
+      asm volatile("cp.async.wait_group 1;" ::: "memory");
+    } else {
+      asm volatile("cp.async.wait_group 0;" ::: "memory");
     }
     __syncthreads();
     // S[16 x 8] of this warp's keys
-    float s[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-    for (int k0 = 0; k0 < DkP; k0 += 32) {
-      uint32_t a[4], a2[4], b[4];
-      ldsm_x4(a, Qs + ((lane & 7) + ((lane >> 3) & 1) * 8) * ld + k0 + (lane >> 4) * 8);
-      ldsm_x4(a2, Qs + ((lane & 7) + ((lane >> 3) & 1) * 8) * ld + k0 + 16 + (lane >> 4) * 8);
-      ldsm_x4(b, Ks + (warp * 8 + (lane & 7)) * ld + k0 + (lane >> 3) * 8);
-      mma_bf16(s, a, b[0], b[1]);
-      mma_bf16(s, a2, b[2], b[3]);
+    float s[4] = {0.0f, 0.0f, 0.0f, 0.0f}, sb[4] = {0.0f, 0.0f, 0.0f, 0.0f};   // two chains
+    {
+      const __nv_bfloat16* qp = Qs + ((lane & 7) + ((lane >> 3) & 1) * 8) * ld + (lane >> 4) * 8;
+      const __nv_bfloat16* kp = Ks + (warp * 8 + (lane & 7)) * ld + (lane >> 3) * 8;
+#pragma unroll 2
+      for (int k0 = 0; k0 < DkP; k0 += 32) {
+        uint32_t a[4], a2[4], b[4];
+        ldsm_x4(a, qp + k0);
+        ldsm_x4(a2, qp + k0 + 16);
+        ldsm_x4(b, kp + k0);
+        mma_bf16(s, a, b[0], b[1]);
+        mma_bf16(sb, a2, b[2], b[3]);
+      }
+      s[0] += sb[0]; s[1] += sb[1]; s[2] += sb[2]; s[3] += sb[3];
     }
     {
       const int key = j0 + warp * 8 + 2 * t;
@@ -354,6 +378,7 @@ latent_attn_mma_kernel(__nv_bfloat16* __restrict__ out, int64_t out_hs, int64_t 
         }
       }
     }
+    __syncthreads();   // this tile's buffer and the score tile are free again
   }
   // epilogue
   const int h0 = hg * kMmaRows + g, h1 = h0 + 8;
@@ -431,7 +456,8 @@ int launch_latent_mma(void* out, int64_t out_hs, int64_t out_ts, float* o_part, 
                       const int* blk_cu, const int* token_seq, int64_t rows, int H, int dim, int rd, int rank,
                       int block_size, float scale, cudaStream_t st) {
   const int DkP = (rank + rd + 31) / 32 * 32, ld = DkP + 8;
-  const size_t smem = ((size_t)(kMmaRows + kTileKeys) * ld + 16) * sizeof(__nv_bfloat16) + kMmaRows * 36 * sizeof(float);
+  const size_t smem = ((size_t)(kMmaRows + 2 * kTileKeys) * ld + 16) * sizeof(__nv_bfloat16) + kMmaRows * 36 * sizeof(float);
+  B200_CHECK_ARG(smem <= 220 * 1024, "latent_attn: rank + rot_dim = %d does not fit in shared memory", rank + rd);
   auto kern = latent_attn_mma_kernel<QA, NTV>;
   if (smem > 48 * 1024)
     B200_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));

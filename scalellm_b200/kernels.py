@@ -736,7 +736,7 @@ def latent_attn_splits(rows: int, n_heads: int, kv_max: int, dtype: torch.dtype,
         return 0
     ctas = rows * ((n_heads + 15) // 16)
     want = -(-2 * 148 // max(ctas, 1))
-    return max(1, min(want, -(-kv_max // 128), 64))
+    return max(1, min(want, -(-kv_max // 64), 64))
 
 
 def latent_attn(q_absorbed: torch.Tensor, q: torch.Tensor, cache: torch.Tensor, q_cu: torch.Tensor,
