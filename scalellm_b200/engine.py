@@ -65,10 +65,10 @@ class Sampler:
             _lib.ensure(("elementwise.cu",))
             return [int(x) for x in kernels.argmax(logits.contiguous()).tolist()]
         _lib.ensure(("elementwise.cu", "sampling.cu"))
-        lg = logits.to(torch.float32).contiguous()
+        lg = logits.to(torch.bfloat16).clone().contiguous()   # the logits processors work in place, in 16 bits
         greedy = kernels.argmax(lg)
         temps = torch.tensor([max(s.sampling.temperature, 1e-6) for s in seqs], dtype=torch.float32,
-                             device=self.device)
+                             device=self.device).to(lg.dtype)
         kernels.apply_temperature_penalty(lg, temps)
         top_k = torch.tensor([s.sampling.top_k for s in seqs], dtype=torch.int64, device=self.device)
         top_p = torch.tensor([s.sampling.top_p for s in seqs], dtype=torch.float32, device=self.device)
@@ -82,7 +82,7 @@ class Sampler:
             g = self._gen.get(s.rid)
             if g is None:
                 g = self._gen[s.rid] = torch.Generator(device=self.device).manual_seed(s.sampling.seed)
-            out.append(int(torch.multinomial(lg[i], 1, generator=g)))
+            out.append(int(torch.multinomial(lg[i].float(), 1, generator=g)))
         return out
 
     def forget(self, rid: str) -> None:

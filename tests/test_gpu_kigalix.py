@@ -332,6 +332,19 @@ def test_greedy_generation_through_the_scheduler():
     assert eng.pool.n_free_blocks() == 40 and not eng.seqs
 
 
+def test_sampled_generation_is_seeded_and_top_k_one_is_greedy():
+    from scalellm_b200.engine import SamplingParams
+    cfg = kc.CONFIGS["one_stream"]
+    model, _ = build(cfg, torch.bfloat16, seed=9)
+    prompts = [toks(9, cfg["vocab"], 1), toks(4, cfg["vocab"], 2)]
+    gen = lambda sp: engine_for(model, max_tokens=128, block_size=4).generate(prompts, sp)
+    greedy = gen([SamplingParams(max_new_tokens=5)] * 2)
+    assert gen([SamplingParams(5, temperature=0.8, top_k=1, seed=3)] * 2) == greedy
+    a = gen([SamplingParams(5, temperature=1.5, top_k=20, top_p=0.95, seed=3), SamplingParams(5, temperature=1.5, seed=4)])
+    b = gen([SamplingParams(5, temperature=1.5, top_k=20, top_p=0.95, seed=3), SamplingParams(5, temperature=1.5, seed=4)])
+    assert a == b and all(0 <= t < cfg["vocab"] for o in a for t in o)
+
+
 def test_unknown_architecture_and_layer_type_are_refused():
     from scalellm_b200 import registry
     with pytest.raises(ValueError):
