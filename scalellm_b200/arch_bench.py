@@ -195,6 +195,53 @@ def rooflines(s: dict, batch: int, seqlen: int, k: dict, l: dict, peaks: dict) -
     return out
 
 
+def attention_kernels(s: dict, peaks: dict, cases=((64, 4096, 1), (4, 2048, 2048))) -> dict:
+    """The two designs' attention kernels alone, on caches larger than L2: (batch, cached length, new tokens per
+    sequence) = decoding over long contexts and one prompt portion.  CUDA events around 10 launches after 3."""
+    from . import kernels
+    from .decode_step import BlockPool, StepBuffers, build_step_batch
+    dev = torch.device("cuda", torch.cuda.current_device())
+    hbm, tf = peaks["hbm_gbs"] * 1e9, peaks["bf16_tflops"] * 1e12
+    H, dim, rd, rank = s["heads"], s["dim"], s["rot"], s["rank"]
+    Hl, Hkv, D, bs = s["width"] // 128, max(1, s["width"] // 512), 128, 16
+    out = {}
+    for batch, ctx, q_len in cases:
+        n_blocks = batch * (-(-ctx // bs)) + 8
+        pool = BlockPool(n_blocks, bs, seed=1)
+        seqs = []
+        for _ in range(batch):
+            sq = pool.open_sequence()
+            pool.reserve(sq, ctx)
+            seqs.append(sq)
+        hb = build_step_batch(pool, seqs, [[0] * q_len] * batch, [ctx - q_len] * batch, list(range(batch)))
+        tokens, positions, prm = StepBuffers(dev, batch * q_len, batch, n_blocks).upload(hb)
+        rows = batch * q_len
+        keys = batch * (q_len * (ctx - q_len) + q_len * (q_len + 1) // 2)      # visible (query, key) pairs
+        g = torch.Generator(device=dev).manual_seed(0)
+        rnd = lambda *shape: torch.randn(shape, generator=g, device=dev, dtype=torch.float32).to(torch.bfloat16)
+        cache = rnd(n_blocks * bs, rank + rd)
+        qa, q = rnd(H, rows, rank), rnd(rows, H * (dim + rd))
+        f_lat = lambda: kernels.latent_attn(qa, q, cache, prm.q_cu_seq_lens, prm.kv_cu_seq_lens, prm.block_tables,
+                                            prm.cu_block_lens, prm.token_seq, H, dim, rd, rank, bs, 0.07, ctx)
+        kc, vc = rnd(n_blocks * bs, Hkv, D), rnd(n_blocks * bs, Hkv, D)
+        ql, ol = rnd(rows, Hl, D), torch.empty((rows, Hl, D), dtype=torch.bfloat16, device=dev)
+        f_llama = lambda: kernels.paged_kv_varlen_mha(ol, ql, kc, vc, prm.q_cu_seq_lens, prm.kv_cu_seq_lens,
+                                                      prm.block_tables, prm.cu_block_lens, None, bs, q_len, ctx,
+                                                      D ** -0.5, 0.0, -1)
+        for name, fn, nbytes, flops in (
+                ("kigalix latent_attn", f_lat, batch * ctx * (rank + rd) * 2 + rows * H * (2 * rank + rd) * 2,
+                 keys * H * 2 * (2 * rank + rd)),
+                ("llama paged attention", f_llama, batch * ctx * 2 * Hkv * D * 2 + rows * Hl * D * 4, keys * Hl * 4 * D)):
+            ms = _time_steps(fn, 3, 10)
+            roof = max(nbytes / hbm, flops / tf) * 1e3
+            out[f"{name}, {batch} x {ctx} cached, {q_len} new"] = {
+                "ms": ms, "GB": nbytes / 1e9, "TFLOP": flops / 1e12, "of_copy_peak": nbytes / (ms * 1e-3) / hbm,
+                "of_gemm_peak": flops / (ms * 1e-3) / tf, "roof_ms": roof, "of_roof": roof / ms}
+        del cache, kc, vc
+        torch.cuda.empty_cache()
+    return out
+
+
 def run(args) -> None:
     torch.cuda.set_device(0)
     torch.backends.cuda.matmul.allow_tf32 = False
@@ -213,5 +260,6 @@ def run(args) -> None:
         l = _run_model(llama_config(s), batch, seqlen, args.warmup, args.steps, LLAMA_KERNELS)
         out["sizes"][name] = {"shape": s, "batch": batch, "seq_len": seqlen, "kigalix": k, "llama": l,
                               "kernel_rooflines": rooflines(s, batch, seqlen, k, l, peaks),
+                              "attention_kernels": attention_kernels(s, peaks),
                               "seconds": round(time.time() - t0, 1)}
     print(json.dumps(out))

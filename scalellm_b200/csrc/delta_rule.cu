@@ -25,12 +25,13 @@ delta_rule_kernel(T* __restrict__ out, int64_t ldo, const T* __restrict__ r, con
                   const int* __restrict__ state_slots, int H, int d, float decay_scale, float key_eps,
                   float eps) {
   constexpr int NT = DK < 32 ? 32 : DK;
-  __shared__ float r_s[DK], k_s[DK], u_s[DK], w_s[DK], au_s[DK];
+  __shared__ __align__(16) float r_s[DK], k_s[DK], u_s[DK], w_s[DK], au_s[DK];
   __shared__ float red[32], red2[32];   // alternate: block_sum does not sync after reading
   const int seq = blockIdx.x, h = blockIdx.y, j = threadIdx.x;
   const int t0 = q_cu[seq], t1 = q_cu[seq + 1];
   if (t0 >= t1) return;
   const bool live = j < d;
+  if (j < DK && !live) r_s[j] = k_s[j] = u_s[j] = w_s[j] = au_s[j] = 0.0f;   // padding entries stay zero
   float* Sg = state + (((size_t)state_slots[seq] * H + h) * d) * d;   // [key][value]
   float S[DK];
   const bool fresh = positions[t0] == 0;
@@ -38,40 +39,63 @@ delta_rule_kernel(T* __restrict__ out, int64_t ldo, const T* __restrict__ r, con
   for (int kk = 0; kk < DK; ++kk) S[kk] = (live && kk < d && !fresh) ? Sg[(size_t)kk * d + j] : 0.0f;
   const int c = h * d + j;
   const float w0j = live ? w0[c] : 0.0f, a0j = live ? a0[c] : 0.0f, nwj = live ? nw[c] : 0.0f;
-  for (int t = t0; t < t1; ++t) {
-    const size_t base = (size_t)t * ld + c;
-    float kj = 0.0f, vj = 0.0f;
+  // the six inputs of token t + 1 are loaded while token t is computed: the recurrence itself is short,
+  // a dependent global load per token would dominate it
+  float nk = 0.0f, nv = 0.0f, nr = 0.0f, nwl = 0.0f, nal = 0.0f, ng = 0.0f;
+  auto load_token = [&](int t) {
     if (live) {
-      kj = Num<T>::to_f(k[base]);
-      vj = Num<T>::to_f(v[base]);
-      r_s[j] = Num<T>::to_f(r[base]);
+      const size_t base = (size_t)t * ld + c;
+      nk = Num<T>::to_f(k[base]);
+      nv = Num<T>::to_f(v[base]);
+      nr = Num<T>::to_f(r[base]);
+      nal = Num<T>::to_f(al[base]);
+      ng = Num<T>::to_f(g[base]);
+      nwl = Num<T>::to_f(wl[(size_t)t * ld_w + c]);
+    }
+  };
+  load_token(t0);
+  for (int t = t0; t < t1; ++t) {
+    const float kj = nk, vj = nv, alj = nal, gj = ng;
+    if (live) {
+      r_s[j] = nr;
       k_s[j] = kj;
-      const float sw = 1.0f / (1.0f + expf(-(Num<T>::to_f(wl[(size_t)t * ld_w + c]) + w0j)));
+      const float sw = 1.0f / (1.0f + expf(-(nwl + w0j)));
       w_s[j] = expf(-decay_scale * sw);
     }
+    if (t + 1 < t1) load_token(t + 1);
     const float k2 = block_sum<NT>(kj * kj, red);   // syncs: the vectors above are visible after it
     if (live) {
       const float uj = kj * rsqrtf(k2 + key_eps);
-      const float aj = 1.0f / (1.0f + expf(-(Num<T>::to_f(al[base]) + a0j)));
+      const float aj = 1.0f / (1.0f + expf(-(alj + a0j)));
       u_s[j] = uj;
       au_s[j] = aj * uj;
     }
     __syncthreads();
-    float uS = 0.0f;
+    // both passes over the key dimension read the shared vectors four at a time and keep four partial sums, so
+    // that neither the shared-memory loads nor one long chain of dependent FMAs set the pace (entries >= d are 0)
+    float us4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll
-    for (int kk = 0; kk < DK; ++kk)
-      if (kk < d) uS += u_s[kk] * S[kk];
-    float o = 0.0f;
-#pragma unroll
-    for (int kk = 0; kk < DK; ++kk) {
-      if (kk < d) {
-        S[kk] = w_s[kk] * S[kk] - au_s[kk] * uS + k_s[kk] * vj;
-        o += S[kk] * r_s[kk];
-      }
+    for (int kk = 0; kk < DK; kk += 4) {
+      const float4 u4 = *reinterpret_cast<const float4*>(u_s + kk);
+      us4[0] += u4.x * S[kk]; us4[1] += u4.y * S[kk + 1]; us4[2] += u4.z * S[kk + 2]; us4[3] += u4.w * S[kk + 3];
     }
+    const float uS = (us4[0] + us4[1]) + (us4[2] + us4[3]);
+    float o4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+    for (int kk = 0; kk < DK; kk += 4) {
+      const float4 w4 = *reinterpret_cast<const float4*>(w_s + kk);
+      const float4 a4 = *reinterpret_cast<const float4*>(au_s + kk);
+      const float4 k4 = *reinterpret_cast<const float4*>(k_s + kk);
+      const float4 r4 = *reinterpret_cast<const float4*>(r_s + kk);
+      S[kk] = w4.x * S[kk] - a4.x * uS + k4.x * vj;             o4[0] += S[kk] * r4.x;
+      S[kk + 1] = w4.y * S[kk + 1] - a4.y * uS + k4.y * vj;     o4[1] += S[kk + 1] * r4.y;
+      S[kk + 2] = w4.z * S[kk + 2] - a4.z * uS + k4.z * vj;     o4[2] += S[kk + 2] * r4.z;
+      S[kk + 3] = w4.w * S[kk + 3] - a4.w * uS + k4.w * vj;     o4[3] += S[kk + 3] * r4.w;
+    }
+    const float o = (o4[0] + o4[1]) + (o4[2] + o4[3]);
     const float o2 = block_sum<NT>(live ? o * o : 0.0f, red2);   // also fences the smem vectors
     if (live) {
-      const float gate = 1.0f / (1.0f + expf(-Num<T>::to_f(g[base])));
+      const float gate = 1.0f / (1.0f + expf(-gj));
       out[(size_t)t * ldo + c] = Num<T>::from_f(o * rsqrtf(o2 / (float)d + eps) * nwj * gate);
     }
   }
