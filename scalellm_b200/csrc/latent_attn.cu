@@ -263,17 +263,21 @@ latent_attn_mma_kernel(__nv_bfloat16* __restrict__ out, int64_t out_hs, int64_t 
   const int rank8 = (rank + 7) / 8 * 8;
   // the tile's rows arrive by 16-byte asynchronous copies into one of two buffers: tile i + 1 is in flight
   // while tile i is used.  Rows beyond the last visible key and the padding chunks are zero-filled (size 0).
+  const uint32_t lane_dst = lane * 16;                       // byte offset of this lane's first chunk in a row
   auto fetch = [&](int tile, __nv_bfloat16* Kd) {
-    const int j0 = tile * kTileKeys;
-    for (int jj = warp; jj < kTileKeys; jj += 4) {
-      const int key = j0 + jj;
-      const bool vis = key <= pos;
-      const __nv_bfloat16* src = cache + (vis ? ((size_t)table[key / block_size] + key % block_size) * ldc : 0);
-      for (int c = lane; c < chunks; c += 32) {
-        const bool real = vis && c * 8 < Dk;
-        const uint32_t dst = smem_u32(Kd + jj * ld + c * 8);
-        const int nbytes = real ? 16 : 0;
-        asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(real ? src + c * 8 : cache), "r"(nbytes) : "memory");
+    // lanes 0..7 resolve this warp's eight keys (row warp + 4 i of the tile) through the block table, once
+    const int my_key = tile * kTileKeys + warp + 4 * (lane & 7);
+    long long my_off = -1;
+    if (my_key <= pos) my_off = ((long long)table[my_key / block_size] + my_key % block_size) * ldc;
+    const uint32_t kd = smem_u32(Kd) + lane_dst;
+#pragma unroll
+    for (int i = 0; i < kTileKeys / 4; ++i) {
+      const long long off = __shfl_sync(0xffffffffu, my_off, i);
+      const __nv_bfloat16* src = cache + (off >= 0 ? off : 0) + lane * 8;
+      const uint32_t dst = kd + (uint32_t)(warp + 4 * i) * (uint32_t)(ld * 2);
+      for (int c = lane, it = 0; c < chunks; c += 32, ++it) {
+        const int nbytes = (off >= 0 && c * 8 < Dk) ? 16 : 0;
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst + it * 512), "l"(nbytes ? src + it * 256 : cache), "r"(nbytes) : "memory");
       }
     }
     asm volatile("cp.async.commit_group;" ::: "memory");

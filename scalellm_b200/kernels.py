@@ -731,12 +731,12 @@ def latent_prepare(q: torch.Tensor, dkv: torch.Tensor, cache: torch.Tensor, c_no
 def latent_attn_splits(rows: int, n_heads: int, kv_max: int, dtype: torch.dtype, width: int) -> int:
     """How the keys of a row are cut over CTAs.  0: the CUDA-core kernel (fp32 models, rows that are not
     16-byte multiples, B200_LATENT_IMPL=simt).  Otherwise the tensor-core kernel with enough key ranges to
-    give every SM about two CTAs when the step has few rows (decoding), one range when it has many."""
+    fill (and not overflow) the two CTAs an SM holds when the step has few rows (decoding), one range otherwise."""
     if dtype != torch.bfloat16 or width % 8 or os.environ.get("B200_LATENT_IMPL") == "simt":
         return 0
     ctas = rows * ((n_heads + 15) // 16)
-    want = -(-2 * 148 // max(ctas, 1))
-    return max(1, min(want, -(-kv_max // 64), 64))
+    resident = 2 * 148                    # two CTAs of this kernel fit on an SM; stay within one wave of them
+    return max(1, min(resident // max(ctas, 1), -(-kv_max // 64), 64))
 
 
 def latent_attn(q_absorbed: torch.Tensor, q: torch.Tensor, cache: torch.Tensor, q_cu: torch.Tensor,
