@@ -189,10 +189,10 @@ int dispatch_nr(int rank, void* out, int64_t out_hs, int64_t out_ts, const void*
 // ---------------------------------------------------------------------------------------------
 // Tensor-core form (bf16 cache): one CTA per (token, group of 16 heads, split of the keys), 4 warps.
 // Per 32-key tile: warp w forms S for keys 8w..8w+7 (mma.m16n8k16 over the key width, Q and the
-// tile in shared memory, fragments by ldmatrix), the scaled and masked scores meet in shared memory,
-// every warp redoes the (cheap) online softmax in fp32 and multiplies P by its own quarter of the
-// latent columns (the tile read transposed by ldmatrix.trans).  P enters the tensor core as two
-// bf16 terms, hi + lo, so the weights keep 16 bits of mantissa.  With more than one split each CTA
+// tile in shared memory, fragments by ldmatrix) and does the online softmax of those 8 keys in fp32
+// (the warps' row maxima and sums meet in shared memory); the weights P go to shared memory and every
+// warp multiplies them by its own quarter of the latent columns (the tile read transposed by
+// ldmatrix.trans).  P enters the tensor core as two bf16 terms, hi + lo: 16 bits of mantissa.  With more than one split each CTA
 // writes an unnormalised partial (fp32) with its running maximum and sum; latent_combine merges them.
 // ---------------------------------------------------------------------------------------------
 constexpr int kMmaRows = 16;
@@ -230,8 +230,11 @@ latent_attn_mma_kernel(__nv_bfloat16* __restrict__ out, int64_t out_hs, int64_t 
   const int Dk = rank + rd, DkP = (Dk + 31) / 32 * 32, ld = DkP + 8;
   __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(smem_raw);   // [16][ld]
   __nv_bfloat16* Kbuf = Qs + kMmaRows * ld;                         // 2 x [32][ld], + 16 slack
-  float* Ss = reinterpret_cast<float*>(Kbuf + 2 * kTileKeys * ld + 16);   // [16][36]
-  constexpr int lds = 36;
+  constexpr int ldp = 40;                                                   // 32 keys + 8 of padding
+  __nv_bfloat16* Ph = Kbuf + 2 * kTileKeys * ld + 16;                       // [16][ldp] weights, high part
+  __nv_bfloat16* Pl = Ph + kMmaRows * ldp;                                  // [16][ldp] weights, low part
+  float* Wmax = reinterpret_cast<float*>(Pl + kMmaRows * ldp);              // [16][4] row maximum per warp
+  float* Wsum = Wmax + kMmaRows * 4;                                        // [16][4] row sum per warp
   const int row = blockIdx.x, hg = blockIdx.y, z = blockIdx.z;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
   const int seq = token_seq[row];
@@ -309,60 +312,65 @@ latent_attn_mma_kernel(__nv_bfloat16* __restrict__ out, int64_t out_hs, int64_t 
       }
       s[0] += sb[0]; s[1] += sb[1]; s[2] += sb[2]; s[3] += sb[3];
     }
+    // online softmax, each warp for its own 8 keys: local row maxima meet in shared memory, the weights go
+    // back there as two bf16 terms (hi + lo) and every warp reads them as the A operand of P V
+    float sv[4];
     {
       const int key = j0 + warp * 8 + 2 * t;
       const bool v0 = key <= pos, v1 = key + 1 <= pos;
       const bool r0 = hg * kMmaRows + g < H, r1 = hg * kMmaRows + g + 8 < H;
-      float* s0 = Ss + g * lds + warp * 8 + 2 * t;
-      float* s1 = Ss + (g + 8) * lds + warp * 8 + 2 * t;
-      s0[0] = (v0 && r0) ? s[0] * scale : -INFINITY;
-      s0[1] = (v1 && r0) ? s[1] * scale : -INFINITY;
-      s1[0] = (v0 && r1) ? s[2] * scale : -INFINITY;
-      s1[1] = (v1 && r1) ? s[3] * scale : -INFINITY;
+      sv[0] = (v0 && r0) ? s[0] * scale : -INFINITY;
+      sv[1] = (v1 && r0) ? s[1] * scale : -INFINITY;
+      sv[2] = (v0 && r1) ? s[2] * scale : -INFINITY;
+      sv[3] = (v1 && r1) ? s[3] * scale : -INFINITY;
     }
-    __syncthreads();
-    // online softmax of rows g and g + 8 (every warp the same), P as A fragments: keys 16 kk + {2t, 2t+1, 2t+8, 2t+9}
-    float p0[8], p1[8];
-#pragma unroll
-    for (int kk = 0; kk < 2; ++kk) {
-#pragma unroll
-      for (int hh = 0; hh < 2; ++hh) {
-        const float2 x0 = *reinterpret_cast<const float2*>(Ss + g * lds + 16 * kk + 8 * hh + 2 * t);
-        const float2 x1 = *reinterpret_cast<const float2*>(Ss + (g + 8) * lds + 16 * kk + 8 * hh + 2 * t);
-        p0[kk * 4 + hh * 2] = x0.x; p0[kk * 4 + hh * 2 + 1] = x0.y;
-        p1[kk * 4 + hh * 2] = x1.x; p1[kk * 4 + hh * 2 + 1] = x1.y;
-      }
-    }
-    float mx0 = -INFINITY, mx1 = -INFINITY;
-#pragma unroll
-    for (int i = 0; i < 8; ++i) { mx0 = fmaxf(mx0, p0[i]); mx1 = fmaxf(mx1, p1[i]); }
+    float mx0 = fmaxf(sv[0], sv[1]), mx1 = fmaxf(sv[2], sv[3]);
 #pragma unroll
     for (int o = 1; o <= 2; o <<= 1) {
       mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, o));
       mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, o));
     }
-    const float n0 = fmaxf(m0, mx0), n1 = fmaxf(m1, mx1);
-    const float c0 = (n0 == -INFINITY) ? 1.0f : expf(m0 - n0), c1 = (n1 == -INFINITY) ? 1.0f : expf(m1 - n1);
-    float sum0 = 0.0f, sum1 = 0.0f;
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      p0[i] = (n0 == -INFINITY) ? 0.0f : expf(p0[i] - n0);
-      p1[i] = (n1 == -INFINITY) ? 0.0f : expf(p1[i] - n1);
-      sum0 += p0[i]; sum1 += p1[i];
-    }
+    if (t == 0) { Wmax[g * 4 + warp] = mx0; Wmax[(g + 8) * 4 + warp] = mx1; }
+    __syncthreads();
+    const float4 wm0 = *reinterpret_cast<const float4*>(Wmax + g * 4);
+    const float4 wm1 = *reinterpret_cast<const float4*>(Wmax + (g + 8) * 4);
+    const float n0 = fmaxf(m0, fmaxf(fmaxf(wm0.x, wm0.y), fmaxf(wm0.z, wm0.w)));
+    const float n1 = fmaxf(m1, fmaxf(fmaxf(wm1.x, wm1.y), fmaxf(wm1.z, wm1.w)));
+    const bool e0 = n0 == -INFINITY, e1 = n1 == -INFINITY;       // nothing visible yet (padding rows)
+    const float pa = e0 ? 0.0f : expf(sv[0] - n0), pb = e0 ? 0.0f : expf(sv[1] - n0);
+    const float pc = e1 ? 0.0f : expf(sv[2] - n1), pd = e1 ? 0.0f : expf(sv[3] - n1);
+    float sum0 = pa + pb, sum1 = pc + pd;
 #pragma unroll
     for (int o = 1; o <= 2; o <<= 1) {
       sum0 += __shfl_xor_sync(0xffffffffu, sum0, o);
       sum1 += __shfl_xor_sync(0xffffffffu, sum1, o);
     }
-    l0 = l0 * c0 + sum0; l1 = l1 * c1 + sum1; m0 = n0; m1 = n1;
+    if (t == 0) { Wsum[g * 4 + warp] = sum0; Wsum[(g + 8) * 4 + warp] = sum1; }
+    {
+      uint32_t hi, lo;
+      split_bf16(pa, pb, hi, lo);
+      *reinterpret_cast<uint32_t*>(Ph + g * ldp + warp * 8 + 2 * t) = hi;
+      *reinterpret_cast<uint32_t*>(Pl + g * ldp + warp * 8 + 2 * t) = lo;
+      split_bf16(pc, pd, hi, lo);
+      *reinterpret_cast<uint32_t*>(Ph + (g + 8) * ldp + warp * 8 + 2 * t) = hi;
+      *reinterpret_cast<uint32_t*>(Pl + (g + 8) * ldp + warp * 8 + 2 * t) = lo;
+    }
+    __syncthreads();
+    const float c0 = e0 ? 1.0f : expf(m0 - n0), c1 = e1 ? 1.0f : expf(m1 - n1);
+    {
+      const float4 ws0 = *reinterpret_cast<const float4*>(Wsum + g * 4);
+      const float4 ws1 = *reinterpret_cast<const float4*>(Wsum + (g + 8) * 4);
+      l0 = l0 * c0 + ((ws0.x + ws0.y) + (ws0.z + ws0.w));
+      l1 = l1 * c1 + ((ws1.x + ws1.y) + (ws1.z + ws1.w));
+      m0 = n0; m1 = n1;
+    }
     uint32_t ph[2][4], pl[2][4];
-#pragma unroll
-    for (int kk = 0; kk < 2; ++kk) {
-      split_bf16(p0[kk * 4 + 0], p0[kk * 4 + 1], ph[kk][0], pl[kk][0]);   // row g,     keys 2t, 2t+1
-      split_bf16(p1[kk * 4 + 0], p1[kk * 4 + 1], ph[kk][1], pl[kk][1]);   // row g + 8
-      split_bf16(p0[kk * 4 + 2], p0[kk * 4 + 3], ph[kk][2], pl[kk][2]);   // row g,     keys 2t+8, 2t+9
-      split_bf16(p1[kk * 4 + 2], p1[kk * 4 + 3], ph[kk][3], pl[kk][3]);
+    {
+      const int prow = (lane & 7) + ((lane >> 3) & 1) * 8, pcol = (lane >> 4) * 8;
+      ldsm_x4(ph[0], Ph + prow * ldp + pcol);
+      ldsm_x4(ph[1], Ph + prow * ldp + 16 + pcol);
+      ldsm_x4(pl[0], Pl + prow * ldp + pcol);
+      ldsm_x4(pl[1], Pl + prow * ldp + 16 + pcol);
     }
 #pragma unroll
     for (int nt = 0; nt < NTV; nt += 2) {
@@ -460,7 +468,8 @@ int launch_latent_mma(void* out, int64_t out_hs, int64_t out_ts, float* o_part, 
                       const int* blk_cu, const int* token_seq, int64_t rows, int H, int dim, int rd, int rank,
                       int block_size, float scale, cudaStream_t st) {
   const int DkP = (rank + rd + 31) / 32 * 32, ld = DkP + 8;
-  const size_t smem = ((size_t)(kMmaRows + 2 * kTileKeys) * ld + 16) * sizeof(__nv_bfloat16) + kMmaRows * 36 * sizeof(float);
+  const size_t smem = ((size_t)(kMmaRows + 2 * kTileKeys) * ld + 16 + 2 * kMmaRows * 40) * sizeof(__nv_bfloat16) +
+                      2 * kMmaRows * 4 * sizeof(float);
   B200_CHECK_ARG(smem <= 220 * 1024, "latent_attn: rank + rot_dim = %d does not fit in shared memory", rank + rd);
   auto kern = latent_attn_mma_kernel<QA, NTV>;
   if (smem > 48 * 1024)
