@@ -27,7 +27,7 @@
 //     world slots in rank order in fp32 (bit-identical to the one-shot result and to a host sum in
 //     rank order), rounds once and pushes the reduced chunk into every rank's result buffer; every
 //     rank then consumes the row from its own memory.  Every block of every rank sends and reduces
-//     the same amount (the first cut of this round partitioned by rows: 8 of a rank's 64 blocks did
+//     the same amount (an earlier cut partitioned by rows: 8 of a rank's 64 blocks did
 //     all of its reducing and 7x the sending, 15.9 us per fused call at 8 ranks against 9.6 at 2).
 //     Per rank and call NVLink carries (world-1)/world of the message out and the same in, twice —
 //     0.9 MB at 8 ranks instead of the one-shot's 3.7 MB pull — and the critical path is two

@@ -473,7 +473,7 @@ __device__ __forceinline__ void pdl_launch_dependents() {
 // Sum of the partial slots of 8 consecutive columns (one 32-byte group inside one n tile) of
 // row `row_ptr`: the loads of the `count` contributing slots are all issued up front (one L2 round
 // trip; absent slots are neither loaded — they may hold stale NaNs — nor added), fixed summation
-// order ((p0 + p1) + p2) + ...  Round 1 loaded all 8 slots with the absent ones clamped onto the
+// order ((p0 + p1) + p2) + ...  An earlier version loaded all 8 slots with the absent ones clamped onto the
 // last one: 4x the L2 traffic at the usual 2 contributors — the gate_up consumer spent 14.7 us
 // on it (profiles/r02_step_timeline.md).
 __device__ __forceinline__ void w4_sum_partials8(float (&a)[8], const float* __restrict__ p0,

@@ -765,8 +765,8 @@ constexpr int ATT_P_TPS_MAX = 32;                            // tiles per item (
 constexpr int ATT_P_TBL = ATT_P_TPS_MAX * ATT_TILE + 8;      // block-table window entries (bs = 1)
 // Occupancy variant (OCC = 1, B200_ATTN_OCC=1): the warp-state profile of the default variant
 // shows warps waiting on their own instruction latencies 60 % of the time and on KV data 5 %
-// (profiles/r01_ncu_paged_attn_stalls.md), i.e. it is latency bound at 7 warps per SM.  Round 2
-// measured the first cut of this variant (2 TMA stages, 11 CTAs per SM): 114.8 us vs 96.6 us —
+// (ncu warp-state counters), i.e. it is latency bound at 7 warps per SM.  A measurement
+// of the first cut of this variant (2 TMA stages, 11 CTAs per SM): 114.8 us vs 96.6 us —
 // the shallower ring costs more than the extra warps give (profiles/r02_attn_variants.md).  What
 // is left of it: the full 3-stage ring with a 264-entry block-table window, which fits 8 instead
 // of 7 one-warp CTAs into an SM's shared memory.
@@ -1509,7 +1509,7 @@ static int attn_occ() {
 }
 
 // Transposed-tile instantiation of the stream kernel (TR above) for shapes whose packed rows fit
-// 8: group * max_q_len <= 8 (decode), head_dim <= 128.  Default since round 2 (91.2 us vs 96.6 us
+// 8: group * max_q_len <= 8 (decode), head_dim <= 128.  Default (91.2 us vs 96.6 us
 // at the benchmark shape, profiles/r02_attn_variants.md); B200_ATTN_TR=0 selects the 16-row tile.
 static int attn_tr() {
   static const int v = [] {

@@ -417,7 +417,7 @@ __device__ __forceinline__ uint32_t lds_u8(uint32_t addr) {
 // bytes pulled out of L2 per weight tile drop by NSUB (the kernel is L2-bandwidth bound on them:
 // every CTA re-reads the [MT x 128] activation tile of each of its k tiles).
 //
-// Round 2 measured ten variants of the MMA loop (one commit per tile, tiles issued in pairs, three
+// Ten variants of the MMA loop (one commit per tile, tiles issued in pairs, three
 // dequant groups, one "full" barrier per stage, two issuing warps and their combinations): all
 // within 3 % of this form on every projection shape (profiles/r02_w4_variants.md), so they are gone.
 template <int MT, int NSUB, bool TRACE>

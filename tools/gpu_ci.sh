@@ -7,7 +7,7 @@ cd "$(dirname "$0")/.."
 mkdir -p gpurun_out
 OUT=gpurun_out
 STAGES="${*:-tests probe smoke bench ncu}"
-# "round2" = everything that was staged after round 1's GPU budget ran out, in one call
+# "round2" = the staged follow-up measurements (timeline, trace, microbenchmarks, occupancy variant, reference kernels) in one call
 if [[ " $STAGES " == *" round2 "* ]]; then
   STAGES="$STAGES tests smoke bench staged timeline trace micro occ refk"
 fi
