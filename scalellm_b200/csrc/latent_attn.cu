@@ -181,8 +181,9 @@ int dispatch_nr(int rank, void* out, int64_t out_hs, int64_t out_ts, const void*
   if (nr <= 4) return launch_latent_attn<T, QA, 4>(LA_ARGS);
   if (nr <= 8) return launch_latent_attn<T, QA, 8>(LA_ARGS);
   if (nr <= 16) return launch_latent_attn<T, QA, 16>(LA_ARGS);
+  if (nr <= 32) return launch_latent_attn<T, QA, 32>(LA_ARGS);
 #undef LA_ARGS
-  return set_error(B200_ERR_UNSUPPORTED, "latent_attn: latent rank %d > 512", rank);
+  return set_error(B200_ERR_UNSUPPORTED, "latent_attn: latent rank %d > 1024", rank);
 }
 
 
@@ -502,7 +503,8 @@ int dispatch_mma(int rank, void* out, int64_t out_hs, int64_t out_ts, float* o_p
   if (need <= 8) return launch_latent_mma<QA, 8>(LM_ARGS);
   if (need <= 16) return launch_latent_mma<QA, 16>(LM_ARGS);
 #undef LM_ARGS
-  return set_error(B200_ERR_UNSUPPORTED, "latent_attn: latent rank %d > 512", rank);
+  return set_error(B200_ERR_UNSUPPORTED, "latent_attn: the tensor-core form takes latent ranks up to 512 (got %d); "
+                   "pass n_splits = 0", rank);
 }
 
 }  // namespace

@@ -481,6 +481,7 @@ class StepBuffers:
         self.host = torch.zeros(total, dtype=torch.int32, pin_memory=torch.cuda.is_available())
         self.host_np = self.host.numpy()
         self.dev = torch.zeros(total, dtype=torch.int32, device=device)
+        self._copied: Optional[torch.cuda.Event] = None   # the last staging copy (see upload)
 
     def h2d_bytes(self, hb: HostBatch) -> int:
         """Bytes of the single staging copy a step performs (up to the end of the block table)."""
@@ -493,6 +494,8 @@ class StepBuffers:
                 "token_seq": hb.token_seq if hb.token_seq is not None else hb.tokens[:0],
                 "state_slots": hb.state_slots if hb.state_slots is not None else hb.tokens[:0],
                 "tables": hb.block_tables}
+        if self._copied is not None:      # the pinned buffer is reused: the previous step's copy must have read it
+            self._copied.synchronize()
         view = {}
         for f in self.FIELDS:
             o, cap = self.off[f]
@@ -502,6 +505,9 @@ class StepBuffers:
             view[f] = self.dev[o:o + n]
         used = self.off["tables"][0] + len(hb.block_tables)
         self.dev[:used].copy_(self.host[:used], non_blocking=True)
+        if self.dev.is_cuda:
+            self._copied = torch.cuda.Event()
+            self._copied.record()
         B = len(hb.q_cu_lens) - 1
         params = InputParameters(
             num_sequences=B, q_cu_seq_lens=view["q_cu"], kv_cu_seq_lens=view["kv_cu"],

@@ -728,11 +728,11 @@ def latent_prepare(q: torch.Tensor, dkv: torch.Tensor, cache: torch.Tensor, c_no
                                           _stream()))
 
 
-def latent_attn_splits(rows: int, n_heads: int, kv_max: int, dtype: torch.dtype, width: int) -> int:
+def latent_attn_splits(rows: int, n_heads: int, kv_max: int, dtype: torch.dtype, width: int, rank: int = 0) -> int:
     """How the keys of a row are cut over CTAs.  0: the CUDA-core kernel (fp32 models, rows that are not
     16-byte multiples, B200_LATENT_IMPL=simt).  Otherwise the tensor-core kernel with enough key ranges to
     fill (and not overflow) the two CTAs an SM holds when the step has few rows (decoding), one range otherwise."""
-    if dtype != torch.bfloat16 or width % 8 or os.environ.get("B200_LATENT_IMPL") == "simt":
+    if dtype != torch.bfloat16 or width % 8 or rank > 512 or os.environ.get("B200_LATENT_IMPL") == "simt":
         return 0
     ctas = rows * ((n_heads + 15) // 16)
     resident = 2 * 148                    # two CTAs of this kernel fit on an SM; stay within one wave of them
@@ -752,7 +752,7 @@ def latent_attn(q_absorbed: torch.Tensor, q: torch.Tensor, cache: torch.Tensor, 
     assert q_absorbed.shape == (n_heads, rows, rank) and q_absorbed.stride(2) == 1
     assert q_absorbed.dtype in (torch.float32, q.dtype) and q.stride(1) == 1 and cache.dtype == q.dtype
     out = torch.empty((n_heads, rows, rank), dtype=q.dtype, device=q.device)
-    splits = latent_attn_splits(rows, n_heads, kv_max, q.dtype, rank + rot_dim) if cache.stride(0) % 8 == 0 else 0
+    splits = latent_attn_splits(rows, n_heads, kv_max, q.dtype, rank + rot_dim, rank) if cache.stride(0) % 8 == 0 else 0
     ws, ws_bytes = None, 0
     if splits > 1:
         ws_bytes = int(_lib.load().b200_latent_attn_workspace_bytes(rows, n_heads, rank, splits))

@@ -345,6 +345,23 @@ def test_sampled_generation_is_seeded_and_top_k_one_is_greedy():
     assert a == b and all(0 <= t < cfg["vocab"] for o in a for t in o)
 
 
+def test_llama_runs_through_the_same_engine():
+    """The Llama decoder behind the registry and the engine: a prompt in portions plus decoded tokens gives
+    the logits of the whole prompt in one step (same kernels, other cuts), and blocks are reused."""
+    from scalellm_b200 import registry
+    cfg = {"architectures": ["LlamaForCausalLM"], "hidden_size": 256, "num_hidden_layers": 2,
+           "num_attention_heads": 2, "num_key_value_heads": 1, "intermediate_size": 512, "vocab_size": 512,
+           "rope_theta": 10000.0, "rms_norm_eps": 1e-5, "max_position_embeddings": 512, "rope_scaling": None}
+    model = registry.create_model(cfg, torch.bfloat16, DEV, max_seqs=2)
+    model.init_random(3)
+    tokens = toks(40, 512, 5)
+    eng = engine_for(model, max_tokens=64, block_size=8, max_seqs=2)
+    whole = run_schedule(eng, tokens, [40])
+    parts = run_schedule(eng, tokens, [9, 17, 2])
+    assert eng.pool.n_free_blocks() == 8 and eng.slots is None
+    assert kc.logits_error(parts, whole) < 3e-2
+
+
 def test_unknown_architecture_and_layer_type_are_refused():
     from scalellm_b200 import registry
     with pytest.raises(ValueError):
