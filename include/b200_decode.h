@@ -553,6 +553,59 @@ B200_API int b200_moe_gather(void* xs, const void* h, int64_t ldh, const int32_t
 B200_API int b200_moe_combine(void* out, const void* Y, int64_t ldy, const int32_t* pos_of_pair, int64_t rows,
                               int64_t W, int64_t top, int dtype, b200_stream_t stream);
 
+/* ---------------------------------------------------------------------------
+ * Decoders with a normalised sublayer RESULT, a depth-weighted average of layer results, a minimal gated
+ * recurrence and differential sliding-window attention (postnorm.cu, mingru.cu, diff_attn.cu).  The reference
+ * has no such operators; each entry states its arithmetic.  Conventions as in the block above.
+ * ------------------------------------------------------------------------ */
+/* x[row] = scale * table[tok] + pair_table[(mul_prev * prev + mul_cur * tok) mod buckets] (row `buckets` of the
+ * pair table when prev_tokens[row] < 0 or prev_tokens is NULL; no pair term when pair_table is NULL);
+ * x fp32 [rows, W], h (nullable) the same rows as T. */
+B200_API int b200_bigram_embed(float* x, void* h /*nullable*/, const void* table, const void* pair_table /*nullable*/,
+                               const int32_t* tokens, const int32_t* prev_tokens /*nullable*/, int64_t rows,
+                               int64_t W, int64_t vocab, int64_t buckets, int64_t mul_prev, int64_t mul_cur,
+                               float scale, int dtype, b200_stream_t stream);
+/* r = x_in + mult * y / sqrt(mean_group(y^2) + eps) * weight, the row cut into `groups` equal consecutive parts.
+ * Without hist: x_out = r.  With hist (fp32 [n_hist, hist_stride], slice j = the result of stage j):
+ * hist[n_hist - 1] = r and x_out = sum_j coef[j] hist[j].  h_out (nullable): x_out as T.  x_out may be x_in. */
+B200_API int b200_postnorm_residual(float* x_out, void* h_out /*nullable*/, const float* x_in, const void* y,
+                                    int64_t ldy, const float* weight, int64_t rows, int64_t W, int64_t groups,
+                                    float mult, float eps, float* hist /*nullable*/, int64_t hist_stride,
+                                    int64_t n_hist, const float* coef /*nullable*/, int dtype, b200_stream_t stream);
+/* out (T) = x / sqrt(mean_group(x^2) + eps) * weight for fp32 rows x [rows, W]. */
+B200_API int b200_group_rms_norm(void* out, const float* x, const float* weight, int64_t rows, int64_t W,
+                                 int64_t groups, float eps, int dtype, b200_stream_t stream);
+/* out[rows, n] = g sigmoid(slope g) (u + 1) with g = min(in[:, :n], limit), u = clamp(in[:, n:2n], -limit, limit). */
+B200_API int b200_glu_clamped(void* out, const void* in, int64_t rows, int64_t n, int64_t ld_in, float limit,
+                              float slope, int dtype, b200_stream_t stream);
+/* out[r, c] = gelu_tanh(in[r, c]) * table[tokens[r], col0 + c] for c < n. */
+B200_API int b200_token_gated_gelu(void* out, const void* in, int64_t ld_in, const void* table, int64_t ld_table,
+                                   int64_t col0, const int32_t* tokens, int64_t rows, int64_t n, int64_t vocab,
+                                   int dtype, b200_stream_t stream);
+/* Minimal gated recurrent unit over each sequence's tokens of the step (see mingru.cu): proj = [z | x | g] column
+ * blocks of `width`, state fp32 [n_slots, width]. */
+B200_API int b200_mingru_scan(void* out, int64_t ldo, const void* proj, int64_t ld, const float* z_bias /*nullable*/,
+                              const float* x_bias /*nullable*/, float* state, const int32_t* q_cu_lens,
+                              const int32_t* positions, const int32_t* state_slots, int64_t n_seq, int64_t width,
+                              int dtype, b200_stream_t stream);
+/* Differential attention, per token (see diff_attn.cu): RMS norm + rotation of the H * 2 query maps into q_out
+ * (fp32 [rows, H, 2, dim]) and, when k_in is given, of the G * 2 key maps into k_cache[slot] ([slots, G, 2 * dim])
+ * with v_in copied to v_cache[slot] ([slots, G, vdim]).  q_in / k_in / v_in: rows of stride ld. */
+B200_API int b200_diff_attn_prepare(float* q_out, const void* q_in, const void* k_in /*nullable*/,
+                                    const void* v_in /*nullable*/, int64_t ld, void* k_cache, void* v_cache,
+                                    const float* q_norm_weight, const float* k_norm_weight,
+                                    const float* inv_freq, float rot_mult, const int32_t* positions,
+                                    const int32_t* slots, int64_t rows, int64_t H, int64_t G, int64_t dim,
+                                    int64_t vdim, int64_t rot_dims, float eps, int dtype, b200_stream_t stream);
+/* out[row, h * vdim + c] = the normalised, gated difference of the two maps' attention results (diff_attn.cu).
+ * window 0: every earlier key is visible; gate (nullable): logits [rows, >= H] of stride ldg. */
+B200_API int b200_diff_attn(void* out, int64_t ldo, const float* q, const void* k_cache, const void* v_cache,
+                            const void* gate /*nullable*/, int64_t ldg, const int32_t* q_cu_lens,
+                            const int32_t* kv_cu_lens, const int32_t* block_tables, const int32_t* cu_block_lens,
+                            const int32_t* token_seq, int64_t rows, int64_t H, int64_t G, int64_t dim,
+                            int64_t vdim, int64_t block_size, float scale, int64_t window, int64_t keep_first,
+                            float lambda, float out_scale, float eps, int dtype, b200_stream_t stream);
+
 #ifdef __cplusplus
 } /* extern "C" */
 #endif

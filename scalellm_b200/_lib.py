@@ -117,13 +117,27 @@ SIGNATURES = {
                                  _int, _vp]),
     "b200_moe_gather": (_int, [_vp, _vp, _i64, _vp, _vp, _i64, _i64, _i64, _int, _vp]),
     "b200_moe_combine": (_int, [_vp, _vp, _i64, _vp, _i64, _i64, _i64, _int, _vp]),
+    # post-norm residual with depth-weighted history, minimal gated recurrence, differential attention
+    # (postnorm.cu, mingru.cu, diff_attn.cu)
+    "b200_bigram_embed": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i64, _f32, _int, _vp]),
+    "b200_postnorm_residual": (_int, [_vp, _vp, _vp, _vp, _i64, _vp, _i64, _i64, _i64, _f32, _f32, _vp, _i64, _i64,
+                                      _vp, _int, _vp]),
+    "b200_group_rms_norm": (_int, [_vp, _vp, _vp, _i64, _i64, _i64, _f32, _int, _vp]),
+    "b200_glu_clamped": (_int, [_vp, _vp, _i64, _i64, _i64, _f32, _f32, _int, _vp]),
+    "b200_token_gated_gelu": (_int, [_vp, _vp, _i64, _vp, _i64, _i64, _vp, _i64, _i64, _i64, _int, _vp]),
+    "b200_mingru_scan": (_int, [_vp, _i64, _vp, _i64, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _int, _vp]),
+    "b200_diff_attn_prepare": (_int, [_vp, _vp, _vp, _vp, _i64, _vp, _vp, _vp, _vp, _vp, _f32, _vp, _vp, _i64, _i64,
+                                      _i64, _i64, _i64, _i64, _f32, _int, _vp]),
+    "b200_diff_attn": (_int, [_vp, _i64, _vp, _vp, _vp, _vp, _i64, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64,
+                              _i64, _i64, _f32, _i64, _i64, _f32, _f32, _f32, _int, _vp]),
 }
 
 # Which source files a partial library needs for a group of entry points.  The whole library
 # (libb200decode.so, every source) serves everything; where it has not been built, `ensure()` compiles
 # just the sources a model asks for into a library of its own.
 ALL_SOURCES = ("runtime.cu", "elementwise.cu", "sampling.cu", "paged_attn.cu", "prefill_attn.cu", "w4a16.cu",
-               "dense.cu", "allreduce.cu", "hyper.cu", "latent_attn.cu", "delta_rule.cu", "moe.cu")
+               "dense.cu", "allreduce.cu", "hyper.cu", "latent_attn.cu", "delta_rule.cu", "moe.cu", "postnorm.cu", "mingru.cu",
+               "diff_attn.cu")
 
 _lib: Optional[C.CDLL] = None
 _lib_sources: frozenset = frozenset()

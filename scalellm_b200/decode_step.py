@@ -317,6 +317,7 @@ class HostBatch:
     kv_max: int
     token_seq: Optional[np.ndarray] = None     # int32 [T]  sequence index (within the step) of every row
     state_slots: Optional[np.ndarray] = None   # int32 [B]  recurrent-state slot of every sequence
+    prev_tokens: Optional[np.ndarray] = None   # int32 [T]  the token before every row, -1 at a sequence's start
 
 
 class BlockPool:
@@ -402,10 +403,12 @@ class StateSlotPool:
 
 
 def build_step_batch(pool: BlockPool, seqs: List[int], new_tokens: List[List[int]], cached: List[int],
-                     state_slots: Optional[List[int]] = None) -> HostBatch:
+                     state_slots: Optional[List[int]] = None, last_tokens: Optional[List[int]] = None) -> HostBatch:
     """One step's InputParameters on the host for given token ids: sequence seqs[i] of the pool has
     cached[i] tokens in the cache and runs new_tokens[i] now (a prompt portion or one decoded token).
-    The pool must already hold blocks for cached[i] + len(new_tokens[i]) tokens (BlockPool.reserve)."""
+    The pool must already hold blocks for cached[i] + len(new_tokens[i]) tokens (BlockPool.reserve).
+    last_tokens[i] (models whose embedding reads the token before): the token that precedes new_tokens[i]
+    in its sequence, -1 if there is none; the step then carries that token for every row."""
     bs = pool.block_size
     B = len(seqs)
     ql = np.asarray([len(t) for t in new_tokens], dtype=np.int64)
@@ -426,9 +429,14 @@ def build_step_batch(pool: BlockPool, seqs: List[int], new_tokens: List[List[int
     tables = table[np.arange(table.shape[1])[None, :] < nb[:, None]] if B else np.zeros(0)
     tokens = np.concatenate([np.asarray(t, dtype=np.int64) for t in new_tokens]) if B else np.zeros(0)
     i32 = lambda x: np.ascontiguousarray(x, dtype=np.int32)
+    prev = None
+    if last_tokens is not None:
+        prev = np.empty(T, dtype=np.int64)
+        prev[1:] = tokens[:-1]
+        prev[q_cu[:-1][ql > 0]] = np.asarray(last_tokens, dtype=np.int64)[ql > 0]
     return HostBatch(i32(tokens), i32(positions), i32(q_cu), i32(kv_cu), i32(slots), i32(tables), i32(blk_cu),
                      int(ql.max()) if B else 0, int(kv.max()) if B else 0, i32(seq_of_tok),
-                     None if state_slots is None else i32(state_slots))
+                     None if state_slots is None else i32(state_slots), None if prev is None else i32(prev))
 
 
 def build_decode_batch(pool: BlockPool, kv_lens: List[int], q_lens: List[int], vocab: int,
@@ -466,12 +474,14 @@ class StepBuffers:
     H2D copies): the seven int32 arrays live at fixed offsets, so a step is ONE host->device copy
     and the device views keep their addresses (CUDA-graph safe)."""
 
-    FIELDS = ("tokens", "positions", "slots", "q_cu", "kv_cu", "blk_cu", "token_seq", "state_slots", "tables")
+    FIELDS = ("tokens", "positions", "slots", "q_cu", "kv_cu", "blk_cu", "token_seq", "state_slots", "prev_tokens",
+              "tables")
 
-    def __init__(self, device, max_tokens: int, max_seqs: int, max_blocks: int):
+    def __init__(self, device, max_tokens: int, max_seqs: int, max_blocks: int, with_prev_tokens: bool = False):
         caps = {"tokens": max_tokens, "positions": max_tokens, "slots": max_tokens,
                 "q_cu": max_seqs + 1, "kv_cu": max_seqs + 1, "blk_cu": max_seqs + 1,
-                "token_seq": max_tokens, "state_slots": max_seqs, "tables": max_blocks}
+                "token_seq": max_tokens, "state_slots": max_seqs,
+                "prev_tokens": max_tokens if with_prev_tokens else 0, "tables": max_blocks}
         self.device = device
         self.off, total = {}, 0
         for f in self.FIELDS:
@@ -493,6 +503,7 @@ class StepBuffers:
                 "q_cu": hb.q_cu_lens, "kv_cu": hb.kv_cu_lens, "blk_cu": hb.cu_block_lens,
                 "token_seq": hb.token_seq if hb.token_seq is not None else hb.tokens[:0],
                 "state_slots": hb.state_slots if hb.state_slots is not None else hb.tokens[:0],
+                "prev_tokens": hb.prev_tokens if hb.prev_tokens is not None else hb.tokens[:0],
                 "tables": hb.block_tables}
         if self._copied is not None:      # the pinned buffer is reused: the previous step's copy must have read it
             self._copied.synchronize()
@@ -514,7 +525,8 @@ class StepBuffers:
             kv_max_seq_len=hb.kv_max, q_max_seq_len=hb.q_max, new_cache_slots=view["slots"],
             block_tables=view["tables"], cu_block_lens=view["blk_cu"],
             token_seq=view["token_seq"] if hb.token_seq is not None else None,
-            state_slots=view["state_slots"] if hb.state_slots is not None else None)
+            state_slots=view["state_slots"] if hb.state_slots is not None else None,
+            prev_tokens=view["prev_tokens"] if hb.prev_tokens is not None else None)
         return view["tokens"], view["positions"], params
 
 

@@ -41,6 +41,7 @@ class Sequence_:
     seq: int                          # index in the BlockPool
     slot: int                         # state slot (-1: the model keeps no recurrent state)
     n_cached: int = 0                 # tokens already run
+    last_token: int = -1              # the last token run (-1: none yet); embeddings that read the token before use it
     prompt: List[int] = field(default_factory=list)
     output: List[int] = field(default_factory=list)
     sampling: SamplingParams = field(default_factory=SamplingParams)
@@ -155,7 +156,8 @@ class Engine:
         self.slots = StateSlotPool(max_seqs) if getattr(model, "needs_state_slots", False) else None
         model.alloc_cache(n_blocks, block_size)
         self.max_step_tokens = max_step_tokens or n_blocks * block_size
-        self.bufs = StepBuffers(self.device, self.max_step_tokens, max_seqs, n_blocks + max_seqs)
+        self.needs_prev = bool(getattr(model, "needs_prev_token", False))
+        self.bufs = StepBuffers(self.device, self.max_step_tokens, max_seqs, n_blocks + max_seqs, self.needs_prev)
         self.seqs: Dict[str, Sequence_] = {}
         self.sampler = Sampler(self.device)
         self.use_graphs = use_graphs and self.device.type == "cuda"
@@ -197,7 +199,8 @@ class Engine:
         if row0 > self.max_step_tokens:
             raise ValueError(f"{row0} tokens in one step; the engine was made for {self.max_step_tokens}")
         hb = build_step_batch(self.pool, [s.seq for s in seqs], [e.tokens for e in entries],
-                              [s.n_cached for s in seqs], [s.slot for s in seqs] if self.slots else None)
+                              [s.n_cached for s in seqs], [s.slot for s in seqs] if self.slots else None,
+                              [s.last_token for s in seqs] if self.needs_prev else None)
         idx = torch.tensor(want, dtype=torch.int32).to(self.device, non_blocking=True)
         if self.use_graphs and row0 == len(entries):
             logits = self._decode_step(hb, idx, want)
@@ -206,6 +209,7 @@ class Engine:
             logits = self.model.forward(tokens, positions, params, last_token_idxes=idx)
         for e, s in zip(entries, seqs):
             s.n_cached += len(e.tokens)
+            s.last_token = int(e.tokens[-1])
         return logits
 
     def _decode_step(self, hb, idx: torch.Tensor, want: List[int]) -> torch.Tensor:

@@ -871,3 +871,144 @@ def moe_combine(y: torch.Tensor, pos_of_pair: torch.Tensor, rows: int, top: int)
     check(_lib.load().b200_moe_combine(_p(out), _p(y), y.stride(0), _p(pos_of_pair), rows, y.shape[1], top,
                                        _dt(y), _stream()))
     return out
+
+
+# ---------------------------------------------------------------------------
+# post-norm residual with a depth-weighted history, clamped GLU, token-gated projection (csrc/postnorm.cu)
+# ---------------------------------------------------------------------------
+def bigram_embed(table: torch.Tensor, pair_table: Optional[torch.Tensor], tokens: torch.Tensor,
+                 prev_tokens: Optional[torch.Tensor], buckets: int, mul_prev: int, mul_cur: int, scale: float,
+                 x_out: Optional[torch.Tensor] = None, want_h: bool = True):
+    """x = scale * table[tok] + pair_table[hash(prev, tok)] as fp32 rows (into x_out when given) and, if asked and
+    the table is not fp32 itself, the same rows in the table's dtype.  Returns (x, h or None)."""
+    _cuda(table, pair_table, tokens, prev_tokens)
+    _check_i32(tokens)
+    assert table.dim() == 2 and table.is_contiguous()
+    assert pair_table is None or (pair_table.is_contiguous() and pair_table.dtype == table.dtype
+                                  and pair_table.shape == (buckets + 1, table.shape[1]))
+    rows, W = tokens.numel(), table.shape[1]
+    x = x_out if x_out is not None else torch.empty((rows, W), dtype=torch.float32, device=table.device)
+    _f32(x)
+    assert x.shape == (rows, W)
+    h = torch.empty((rows, W), dtype=table.dtype, device=table.device) if want_h and table.dtype != torch.float32 else None
+    check(_lib.load().b200_bigram_embed(_p(x), _p(h), _p(table), _p(pair_table), _p(tokens), _p(prev_tokens), rows, W,
+                                        table.shape[0], buckets, mul_prev, mul_cur, scale, _dt(table), _stream()))
+    return x, h
+
+
+def postnorm_residual(x: torch.Tensor, y: torch.Tensor, weight: torch.Tensor, groups: int, mult: float, eps: float,
+                      hist: Optional[torch.Tensor] = None, n_hist: int = 0, coef: Optional[torch.Tensor] = None,
+                      x_out: Optional[torch.Tensor] = None, want_h: bool = True):
+    """x_out (default: x, in place) = x + mult * group_rms_norm(y) * weight; with hist [stages, rows, W] the result
+    is stored as stage n_hist - 1 and x_out becomes sum_j coef[j] hist[j] over the first n_hist stages.
+    Returns (x_out, x_out in y's dtype or None when y is fp32 or it is not asked for)."""
+    _cuda(x, y, weight, hist, coef)
+    _f32(x, weight, hist, coef)
+    rows, W = x.shape
+    assert y.shape == (rows, W) and y.stride(1) == 1
+    out = x if x_out is None else x_out
+    _f32(out)
+    assert hist is None or (hist.dim() == 3 and hist.shape[1:] == (rows, W) and 0 < n_hist <= hist.shape[0]
+                            and coef is not None and coef.numel() >= n_hist)
+    h = torch.empty((rows, W), dtype=y.dtype, device=x.device) if want_h and y.dtype != torch.float32 else None
+    check(_lib.load().b200_postnorm_residual(_p(out), _p(h), _p(x), _p(y), y.stride(0), _p(weight), rows, W, groups,
+                                             mult, eps, _p(hist), rows * W if hist is not None else 0, n_hist,
+                                             _p(coef), _dt(y), _stream()))
+    return out, h
+
+
+def group_rms_norm(x: torch.Tensor, weight: torch.Tensor, groups: int, eps: float, dtype: torch.dtype) -> torch.Tensor:
+    """x / sqrt(mean(x^2) + eps) * weight with one root mean square per group of W / groups channels; x fp32."""
+    _cuda(x, weight)
+    _f32(x, weight)
+    rows, W = x.shape
+    out = torch.empty((rows, W), dtype=dtype, device=x.device)
+    check(_lib.load().b200_group_rms_norm(_p(out), _p(x), _p(weight), rows, W, groups, eps, _DT[dtype], _stream()))
+    return out
+
+
+def glu_clamped(gate_up: torch.Tensor, limit: float, slope: float) -> torch.Tensor:
+    """g sigmoid(slope g) (u + 1) for a [rows, 2n] matrix [gate | up], g = min(gate, limit), u = clamp(up, +-limit)."""
+    _cuda(gate_up)
+    assert gate_up.dim() == 2 and gate_up.stride(1) == 1 and gate_up.shape[1] % 2 == 0
+    n = gate_up.shape[1] // 2
+    out = torch.empty((gate_up.shape[0], n), dtype=gate_up.dtype, device=gate_up.device)
+    check(_lib.load().b200_glu_clamped(_p(out), _p(gate_up), gate_up.shape[0], n, gate_up.stride(0), limit, slope,
+                                       _dt(gate_up), _stream()))
+    return out
+
+
+def token_gated_gelu(a: torch.Tensor, table: torch.Tensor, col0: int, tokens: torch.Tensor) -> torch.Tensor:
+    """gelu_tanh(a [rows, n]) * table[tokens, col0 : col0 + n]."""
+    _cuda(a, table, tokens)
+    _check_i32(tokens)
+    assert a.dim() == 2 and a.stride(1) == 1 and table.dim() == 2 and table.stride(1) == 1 and table.dtype == a.dtype
+    rows, n = a.shape
+    out = torch.empty((rows, n), dtype=a.dtype, device=a.device)
+    check(_lib.load().b200_token_gated_gelu(_p(out), _p(a), a.stride(0), _p(table), table.stride(0), col0,
+                                            _p(tokens), rows, n, table.shape[0], _dt(a), _stream()))
+    return out
+
+
+# ---------------------------------------------------------------------------
+# minimal gated recurrent unit (csrc/mingru.cu)
+# ---------------------------------------------------------------------------
+def mingru_scan(proj: torch.Tensor, z_bias: Optional[torch.Tensor], x_bias: Optional[torch.Tensor],
+                state: torch.Tensor, q_cu: torch.Tensor, positions: torch.Tensor, state_slots: torch.Tensor,
+                n_seq: int, width: int) -> torch.Tensor:
+    """proj [rows, >= 3 width] = [z | x | g]; returns S_t * silu(g_t) [rows, width]; state fp32 [slots, width]."""
+    _cuda(proj, state)
+    _f32(z_bias, x_bias, state)
+    _check_i32(q_cu, positions, state_slots)
+    assert proj.dim() == 2 and proj.stride(1) == 1 and proj.shape[1] >= 3 * width and state.shape[1] == width
+    out = torch.empty((proj.shape[0], width), dtype=proj.dtype, device=proj.device)
+    check(_lib.load().b200_mingru_scan(_p(out), width, _p(proj), proj.stride(0), _p(z_bias), _p(x_bias), _p(state),
+                                       _p(q_cu), _p(positions), _p(state_slots), n_seq, width, _dt(proj), _stream()))
+    return out
+
+
+# ---------------------------------------------------------------------------
+# differential sliding-window attention (csrc/diff_attn.cu)
+# ---------------------------------------------------------------------------
+def diff_attn_prepare(q_in: torch.Tensor, k_in: Optional[torch.Tensor], v_in: Optional[torch.Tensor],
+                      k_cache: Optional[torch.Tensor], v_cache: Optional[torch.Tensor], q_norm_w: torch.Tensor,
+                      k_norm_w: Optional[torch.Tensor], inv_freq: Optional[torch.Tensor], rot_mult: float,
+                      rot_dims: int, positions: torch.Tensor, slots: torch.Tensor, H: int, G: int, dim: int,
+                      vdim: int, eps: float) -> torch.Tensor:
+    """Normalised, rotated queries fp32 [rows, H, 2, dim]; with k_in / v_in (column blocks of the same projection
+    matrix as q_in) the normalised, rotated keys and the values go to the cache rows `slots`."""
+    _cuda(q_in, k_in, v_in, k_cache, v_cache)
+    _f32(q_norm_w, k_norm_w, inv_freq)
+    _check_i32(positions, slots)
+    rows, ld = q_in.shape[0], q_in.stride(0)
+    assert q_in.stride(1) == 1 and q_in.shape[1] == H * 2 * dim
+    if k_in is not None:
+        assert k_in.stride(0) == ld and v_in.stride(0) == ld and k_in.dtype == v_in.dtype == q_in.dtype
+        assert k_cache.dtype == v_cache.dtype == q_in.dtype and k_cache.is_contiguous() and v_cache.is_contiguous()
+        assert k_cache.shape[1:] == (G, 2 * dim) and v_cache.shape[1:] == (G, vdim)
+    q = torch.empty((rows, H, 2, dim), dtype=torch.float32, device=q_in.device)
+    check(_lib.load().b200_diff_attn_prepare(_p(q), _p(q_in), _p(k_in), _p(v_in), ld, _p(k_cache), _p(v_cache),
+                                             _p(q_norm_w), _p(k_norm_w), _p(inv_freq), rot_mult, _p(positions),
+                                             _p(slots), rows, H, G, dim, vdim, rot_dims, eps, _dt(q_in), _stream()))
+    return q
+
+
+def diff_attn(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, gate: Optional[torch.Tensor],
+              q_cu: torch.Tensor, kv_cu: torch.Tensor, block_tables: torch.Tensor, cu_block_lens: torch.Tensor,
+              token_seq: torch.Tensor, block_size: int, scale: float, window: int, keep_first: int, lam: float,
+              out_scale: float, eps: float) -> torch.Tensor:
+    """[rows, H * vdim] in the cache's dtype: (softmax(s1) V - lam softmax(s2) V), RMS-normalised per head, times
+    out_scale and sigmoid(gate [rows, H])."""
+    _cuda(q, k_cache, v_cache, gate)
+    _f32(q)
+    _check_i32(q_cu, kv_cu, block_tables, cu_block_lens, token_seq)
+    rows, H, _, dim = q.shape
+    G, vdim = v_cache.shape[1], v_cache.shape[2]
+    assert gate is None or (gate.shape == (rows, H) and gate.stride(1) == 1 and gate.dtype == k_cache.dtype)
+    out = torch.empty((rows, H * vdim), dtype=k_cache.dtype, device=q.device)
+    check(_lib.load().b200_diff_attn(_p(out), H * vdim, _p(q), _p(k_cache), _p(v_cache), _p(gate),
+                                     gate.stride(0) if gate is not None else 0, _p(q_cu), _p(kv_cu),
+                                     _p(block_tables), _p(cu_block_lens), _p(token_seq), rows, H, G, dim, vdim,
+                                     block_size, scale, window, keep_first, lam, out_scale, eps, _dt(k_cache),
+                                     _stream()))
+    return out

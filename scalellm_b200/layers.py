@@ -45,24 +45,28 @@ class InputParameters:
     # which sequence of the step, and the state slot of every sequence
     token_seq: Optional[torch.Tensor] = None        # int32 [n_tokens]
     state_slots: Optional[torch.Tensor] = None      # int32 [n_seq]
+    # models whose embedding reads the token before: that token for every packed row, -1 at a sequence's start
+    prev_tokens: Optional[torch.Tensor] = None      # int32 [n_tokens]
 
     def to(self, device) -> "InputParameters":
         mv = lambda t: None if t is None else t.to(device)
         return InputParameters(self.num_sequences, mv(self.q_cu_seq_lens), mv(self.kv_cu_seq_lens),
                                self.kv_max_seq_len, self.q_max_seq_len, mv(self.new_cache_slots),
                                mv(self.block_tables), mv(self.cu_block_lens), mv(self.token_seq),
-                               mv(self.state_slots))
+                               mv(self.state_slots), mv(self.prev_tokens))
 
 
 class KVCache:
     """Per-layer K and V tensors [n_blocks*block_size, n_kv_heads, head_dim] (kv_cache.cpp:15-27)."""
 
     def __init__(self, n_blocks: int, block_size: int, n_kv_heads: int, head_dim: int,
-                 dtype: torch.dtype, device):
+                 dtype: torch.dtype, device, value_dim: Optional[int] = None):
+        """value_dim: width of a value head where it differs from the key head's (default: the same)."""
         self._block_size = block_size
         self.key_cache = torch.empty((n_blocks * block_size, n_kv_heads, head_dim), dtype=dtype,
                                      device=device)
-        self.value_cache = torch.empty_like(self.key_cache)
+        self.value_cache = (torch.empty_like(self.key_cache) if value_dim is None else
+                            torch.empty((n_blocks * block_size, n_kv_heads, value_dim), dtype=dtype, device=device))
 
     def block_size(self) -> int:
         return self._block_size
@@ -770,5 +774,122 @@ class SparseMoE:
         gu = kernels.grouped_gemm(h, self.gate_up, offsets, n, sorted_pair, wts.view(-1), self.top)
         y = kernels.grouped_gemm(kernels.gated_act(gu, self.act), self.down, offsets, n)
         return kernels.moe_combine(y, pos_of_pair, rows, self.top)
+
+    __call__ = forward
+
+
+# ---------------------------------------------------------------------------
+# Layers of decoders that normalise each sublayer's result (post-norm on the branch), mix tokens with a
+# minimal gated recurrence or with differential sliding-window attention, and add a per-token learned term.
+# ---------------------------------------------------------------------------
+class PostNormResidual:
+    """x <- x + mult * group_rms_norm(y) * w on an fp32 residual x: the sublayer reads x itself and its RESULT y is
+    normalised (the row in `groups` equal consecutive parts, each with its own root mean square).  With a history
+    [stages, rows, W] the new x becomes stage n_hist - 1 and what the next layer reads is sum_j coef[j] stage_j."""
+
+    def __init__(self, weight: torch.Tensor, groups: int, mult: float, eps: float):
+        self.weight = weight.to(torch.float32).contiguous()
+        self.groups, self.mult, self.eps = groups, mult, eps
+
+    def forward(self, x: torch.Tensor, y: torch.Tensor, x_out: Optional[torch.Tensor] = None,
+                hist: Optional[torch.Tensor] = None, n_hist: int = 0, coef: Optional[torch.Tensor] = None):
+        """Returns (new x fp32, the same rows in y's dtype for the next matrix product — x itself in fp32)."""
+        out, h = kernels.postnorm_residual(x, y, self.weight, self.groups, self.mult, self.eps, hist, n_hist, coef,
+                                           x_out)
+        return out, (h if h is not None else out)
+
+    __call__ = forward
+
+
+class MinGRUMixer:
+    """z = sigmoid(Wz h + bz), u = Wx h + bx, c = u + 1/2 (u >= 0) | sigmoid(u); S_t = (1 - z) S_{t-1} + z c per
+    channel (fp32, one state row per sequence slot); out = Wo (S_t * silu(Wg h)).  (csrc/mingru.cu)"""
+
+    def __init__(self, w: Dict[str, torch.Tensor], n_slots: int, dtype: torch.dtype, device):
+        self.width = w["z"].shape[0]
+        self.in_proj = Linear(torch.cat([w["z"], w["x"], w["g"]], dim=0))
+        f = lambda t: None if t is None else t.to(torch.float32).contiguous()
+        self.z_bias, self.x_bias = f(w.get("z.b")), f(w.get("x.b"))
+        self.o_proj = Linear(w["o"])
+        self.state = torch.zeros((n_slots, self.width), dtype=torch.float32, device=device)
+
+    def forward(self, h: torch.Tensor, positions: torch.Tensor, params: InputParameters) -> torch.Tensor:
+        o = kernels.mingru_scan(self.in_proj(h), self.z_bias, self.x_bias, self.state, params.q_cu_seq_lens,
+                                positions, params.state_slots, params.num_sequences, self.width)
+        return self.o_proj(o)
+
+    __call__ = forward
+
+
+class DiffAttention:
+    """Differential attention (csrc/diff_attn.cu): per head two query/key maps [dim] over one set of values [vdim],
+        o = softmax(s1) V - lam softmax(s2) V,  lam = exp(lq1 . lk1) - exp(lq2 . lk2) + diff,
+        o <- o / rms(o) * (1 - diff) * sigmoid(Wg h)_head ; out = Wo concat(o)
+    with per-map RMS norm (one weight [dim] for queries, one for keys) before the rotary turn, a sliding window of
+    `window` keys that also keeps the first `keep_first` tokens visible (window 0: plain causal), and H / G query
+    heads per key/value head.  A layer built without its own k / v weights attends over another layer's cache."""
+
+    def __init__(self, w: Dict[str, torch.Tensor], n_heads: int, n_kv_heads: int, dim: int, vdim: int, scale: float,
+                 window: int, keep_first: int, diff: float, inv_freq: Optional[torch.Tensor], rot_mult: float,
+                 rot_dims: int, eps: float, dtype: torch.dtype, device):
+        self.H, self.G, self.dim, self.vd = n_heads, n_kv_heads, dim, vdim
+        self.scale, self.window, self.keep_first, self.diff = scale, window, keep_first, diff
+        self.rot_mult, self.rot_dims, self.eps, self.dtype = rot_mult, rot_dims, eps, dtype
+        self.inv_freq = None if inv_freq is None else inv_freq.to(torch.float32).to(device).contiguous()
+        self.own_kv = "k" in w
+        parts = [w["q"]] + ([w["k"], w["v"]] if self.own_kv else []) + ([w["g"]] if "g" in w else [])
+        self.has_gate = "g" in w
+        self.in_proj = Linear(torch.cat(parts, dim=0))          # one GEMM for everything that reads h
+        self.q_end = n_heads * 2 * dim
+        self.k_end = self.q_end + (n_kv_heads * 2 * dim if self.own_kv else 0)
+        self.v_end = self.k_end + (n_kv_heads * vdim if self.own_kv else 0)
+        f = lambda t: t.to(torch.float32).contiguous()
+        self.q_norm = f(w["q.norm"])
+        self.k_norm = f(w["k.norm"]) if self.own_kv else None
+        d = lambda a, b: float((w[a].double() * w[b].double()).sum())
+        self.lam = math.exp(d("lq1", "lk1")) - math.exp(d("lq2", "lk2")) + diff
+        self.o_proj = Linear(w["o"])
+
+    def forward(self, h: torch.Tensor, positions: torch.Tensor, cache: KVCache, params: InputParameters) -> torch.Tensor:
+        proj = self.in_proj(h)
+        k_in = proj[:, self.q_end: self.k_end] if self.own_kv else None
+        v_in = proj[:, self.k_end: self.v_end] if self.own_kv else None
+        q = kernels.diff_attn_prepare(proj[:, : self.q_end], k_in, v_in, cache.key_cache if self.own_kv else None,
+                                      cache.value_cache if self.own_kv else None, self.q_norm, self.k_norm,
+                                      self.inv_freq, self.rot_mult, self.rot_dims, positions, params.new_cache_slots,
+                                      self.H, self.G, self.dim, self.vd, self.eps)
+        gate = proj[:, self.v_end: self.v_end + self.H] if self.has_gate else None
+        o = kernels.diff_attn(q, cache.key_cache, cache.value_cache, gate, params.q_cu_seq_lens, params.kv_cu_seq_lens,
+                              params.block_tables, params.cu_block_lens, params.token_seq, cache.block_size(),
+                              self.scale, self.window, self.keep_first, self.lam, 1.0 - self.diff, self.eps)
+        return self.o_proj(o)
+
+    __call__ = forward
+
+
+class ClampedGLU:
+    """down(g * sigmoid(slope * g) * (u + 1)), g = min(gate h, limit), u = clamp(up h, -limit, limit).
+    gate and up share one GEMM."""
+
+    def __init__(self, gate: torch.Tensor, up: torch.Tensor, down: torch.Tensor, limit: float, slope: float):
+        self.gate_up, self.down = Linear(torch.cat([gate, up], dim=0)), Linear(down)
+        self.limit, self.slope = limit, slope
+
+    def forward(self, h: torch.Tensor) -> torch.Tensor:
+        return self.down(kernels.glu_clamped(self.gate_up(h), self.limit, self.slope))
+
+    __call__ = forward
+
+
+class TokenSideInput:
+    """A per-token, per-layer learned vector e = table[token, col0 : col0 + dim] gates a narrow projection of the
+    residual: y = P (gelu_tanh(G h) * e).  (The caller normalises y and adds it.)"""
+
+    def __init__(self, table: torch.Tensor, col0: int, gate: torch.Tensor, proj: torch.Tensor):
+        self.table, self.col0 = table, col0
+        self.gate, self.proj = Linear(gate), Linear(proj)
+
+    def forward(self, h: torch.Tensor, tokens: torch.Tensor) -> torch.Tensor:
+        return self.proj(kernels.token_gated_gelu(self.gate(h), self.table, self.col0, tokens))
 
     __call__ = forward
