@@ -10,7 +10,8 @@ with the reference's per-op rounding made explicit.
 
 ``oracle/kigalix.py`` restates a model the reference does not have (the Kigalix decoder: latent attention,
 delta-rule mixer, sigmoid-routed experts, hyper-connected residual streams) from its equations, one function
-per mechanism, in float64; it is the only yardstick of that path.
+per mechanism, in float64; it is the only yardstick of that path.  ``oracle/pokadra.py`` does the same for the
+Pokadra decoder (post-norm residual with a depth-weighted history, minGRU, differential sliding-window attention).
 
 Pinning: the oracle is checked in ``tests/test_oracle_golden.py``
 against (a) golden vectors generated HERE by importing the reference's own
@@ -32,4 +33,4 @@ computed by the reference's own device functions (``oracle/ref/marlin_dequant_ka
 ``tests/test_gpu_vs_reference_kernels.py`` runs our kernels against them on the same inputs.  The whole engine is not buildable here; see DESIGN.md.
 """
 
-from . import ops, quant, llama, gpt2, kigalix  # noqa: F401
+from . import ops, quant, llama, gpt2, kigalix, pokadra  # noqa: F401

@@ -99,6 +99,26 @@ def diff_lambda(w: Dict[str, torch.Tensor], diff: float) -> float:
     return float(torch.exp((w["lq1"] * w["lk1"]).sum()) - torch.exp((w["lq2"] * w["lk2"]).sum())) + diff
 
 
+def diff_attend(q: torch.Tensor, K: torch.Tensor, V: torch.Tensor, pos: torch.Tensor, scale: float,
+                mask: Optional[dict], lam: float, diff: float, eps: float) -> torch.Tensor:
+    """q [T, H, 2, dim] at positions pos over keys K [n, G, 2, dim] and values V [n, G, vdim] (row j = position j):
+    per head softmax(s1) V - lam softmax(s2) V, divided by its root mean square, times (1 - diff).  [T, H, vdim]"""
+    T, H = q.shape[0], q.shape[1]
+    G = K.shape[1]
+    out = torch.zeros(T, H, V.shape[2], dtype=q.dtype)
+    for t in range(T):
+        i = int(pos[t])
+        js = [j for j in range(i + 1) if visible(i, j, mask)]
+        for hh in range(H):
+            g = hh // (H // G)
+            a = []
+            for mp in range(2):
+                s = (K[js, g, mp, :] @ q[t, hh, mp, :]) * scale
+                a.append(torch.softmax(s, dim=0) @ V[js, g, :])
+            out[t, hh] = rms(a[0] - lam * a[1], eps) * (1.0 - diff)
+    return out
+
+
 def diff_attention(h: torch.Tensor, pos: torch.Tensor, w: Dict[str, torch.Tensor], m: dict, eps: float,
                    kv: dict, shared: Optional[dict]) -> torch.Tensor:
     """kv: this layer's {"k": [n, G, 2, dim], "v": [n, G, vdim]} (grown here unless `shared` — another
@@ -115,22 +135,10 @@ def diff_attention(h: torch.Tensor, pos: torch.Tensor, w: Dict[str, torch.Tensor
         kv["v"] = torch.cat([kv["v"], v]) if "v" in kv else v
     else:
         kv = shared
-    K, V = kv["k"], kv["v"]
-    lam, diff = diff_lambda(w, float(m["diff"])), float(m["diff"])
+    diff = float(m["diff"])
+    o = diff_attend(q, kv["k"], kv["v"], pos, float(m["scale"]), m.get("mask"), diff_lambda(w, diff), diff, eps)
     gate = torch.sigmoid(h @ w["g"].T)                     # [T, H]
-    out = torch.zeros(T, H, vd, dtype=h.dtype)
-    for t in range(T):
-        i = int(pos[t])
-        js = [j for j in range(i + 1) if visible(i, j, m.get("mask"))]
-        for hh in range(H):
-            g = hh // (H // G)
-            a = []
-            for mp in range(2):
-                s = (K[js, g, mp, :] @ q[t, hh, mp, :]) * float(m["scale"])
-                a.append(torch.softmax(s, dim=0) @ V[js, g, :])
-            o = a[0] - lam * a[1]
-            out[t, hh] = rms(o, eps) * (1.0 - diff) * gate[t, hh]
-    return out.reshape(T, H * vd) @ w["o"].T
+    return (o * gate[:, :, None]).reshape(T, H * vd) @ w["o"].T
 
 
 def mingru(h: torch.Tensor, w: Dict[str, torch.Tensor], st: dict) -> torch.Tensor:

@@ -499,11 +499,12 @@ class StepBuffers:
 
     def upload(self, hb: HostBatch) -> Tuple[torch.Tensor, torch.Tensor, InputParameters]:
         """Async H2D of one step's metadata from pinned memory on the current stream."""
+        has_prev = hb.prev_tokens is not None and self.off["prev_tokens"][1] > 0   # buffers made without it drop it
         arrs = {"tokens": hb.tokens, "positions": hb.positions, "slots": hb.new_cache_slots,
                 "q_cu": hb.q_cu_lens, "kv_cu": hb.kv_cu_lens, "blk_cu": hb.cu_block_lens,
                 "token_seq": hb.token_seq if hb.token_seq is not None else hb.tokens[:0],
                 "state_slots": hb.state_slots if hb.state_slots is not None else hb.tokens[:0],
-                "prev_tokens": hb.prev_tokens if hb.prev_tokens is not None else hb.tokens[:0],
+                "prev_tokens": hb.prev_tokens if has_prev else hb.tokens[:0],
                 "tables": hb.block_tables}
         if self._copied is not None:      # the pinned buffer is reused: the previous step's copy must have read it
             self._copied.synchronize()
@@ -526,7 +527,7 @@ class StepBuffers:
             block_tables=view["tables"], cu_block_lens=view["blk_cu"],
             token_seq=view["token_seq"] if hb.token_seq is not None else None,
             state_slots=view["state_slots"] if hb.state_slots is not None else None,
-            prev_tokens=view["prev_tokens"] if hb.prev_tokens is not None else None)
+            prev_tokens=view["prev_tokens"] if has_prev else None)
         return view["tokens"], view["positions"], params
 
 
