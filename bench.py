@@ -60,8 +60,8 @@ def parse():
     ap.add_argument("--layers", type=int, default=None, help="debug only; the default is the named config")
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--skip-cpu-baseline", action="store_true")
-    ap.add_argument("--arch", default="llama", choices=["llama", "kigalix"],
-                    help="kigalix: prefill / decode throughput of the Kigalix design beside the Llama decoder at "
+    ap.add_argument("--arch", default="llama", choices=["llama", "kigalix", "pokadra"],
+                    help="kigalix / pokadra: prefill / decode throughput of that design beside the Llama decoder at "
                          "equal size through the serving engine (scalellm_b200/arch_bench.py); the default "
                          "workload and its JSON line are untouched")
     ap.add_argument("--arch-size", default="all", choices=["all", "w2048", "w4096"])
@@ -702,6 +702,10 @@ def main():
     if a.arch == "kigalix":
         from scalellm_b200 import arch_bench
         arch_bench.run(a)
+        return
+    if a.arch == "pokadra":
+        from scalellm_b200 import arch_bench
+        arch_bench.run_pokadra(a)
         return
     if world != a.gpus and world == 1 and a.gpus > 1:
         print(f"[bench] --gpus {a.gpus} needs torchrun with {a.gpus} ranks; running 1", file=sys.stderr)

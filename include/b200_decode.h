@@ -605,6 +605,17 @@ B200_API int b200_diff_attn(void* out, int64_t ldo, const float* q, const void* 
                             const int32_t* token_seq, int64_t rows, int64_t H, int64_t G, int64_t dim,
                             int64_t vdim, int64_t block_size, float scale, int64_t window, int64_t keep_first,
                             float lambda, float out_scale, float eps, int dtype, b200_stream_t stream);
+/* The same result for prompt portions in bf16 on the tensor cores: CTAs of 16 to 64 consecutive tokens of one
+ * sequence walk tiles of 32 keys (diff_attn.cu).  dim and vdim multiples of 16, at most 128 (..._supported tells);
+ * q_max: the longest portion of the step. */
+B200_API int b200_diff_attn_prefill_supported(int64_t dim, int64_t vdim, int dtype);
+B200_API int b200_diff_attn_prefill(void* out, int64_t ldo, const float* q, const void* k_cache, const void* v_cache,
+                                    const void* gate /*nullable*/, int64_t ldg, const int32_t* q_cu_lens,
+                                    const int32_t* kv_cu_lens, const int32_t* block_tables,
+                                    const int32_t* cu_block_lens, int64_t n_seq, int64_t q_max, int64_t H, int64_t G,
+                                    int64_t dim, int64_t vdim, int64_t block_size, float scale, int64_t window,
+                                    int64_t keep_first, float lambda, float out_scale, float eps, int dtype,
+                                    b200_stream_t stream);
 
 #ifdef __cplusplus
 } /* extern "C" */

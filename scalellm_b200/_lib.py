@@ -130,6 +130,9 @@ SIGNATURES = {
                                       _i64, _i64, _i64, _i64, _f32, _int, _vp]),
     "b200_diff_attn": (_int, [_vp, _i64, _vp, _vp, _vp, _vp, _i64, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64,
                               _i64, _i64, _f32, _i64, _i64, _f32, _f32, _f32, _int, _vp]),
+    "b200_diff_attn_prefill_supported": (_int, [_i64, _i64, _int]),
+    "b200_diff_attn_prefill": (_int, [_vp, _i64, _vp, _vp, _vp, _vp, _i64, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64,
+                                      _i64, _i64, _i64, _f32, _i64, _i64, _f32, _f32, _f32, _int, _vp]),
 }
 
 # Which source files a partial library needs for a group of entry points.  The whole library

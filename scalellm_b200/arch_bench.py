@@ -1,5 +1,5 @@
-"""Prefill and decode throughput of the Kigalix design beside the Llama decoder at equal size
-(`bench.py --arch kigalix`), both through the serving engine, random weights, bf16.
+"""Prefill and decode throughput of the Kigalix and Pokadra designs beside the Llama decoder at equal size
+(`bench.py --arch kigalix|pokadra`), all through the serving engine, random weights, bf16.
 
 Per size: tokens/s of a prompt step (B sequences of L tokens in one batch) and of decode steps (B sequences
 with L cached tokens, one token each), timed with CUDA events after warm-up; and, per kind of kernel, the
@@ -261,5 +261,172 @@ def run(args) -> None:
         out["sizes"][name] = {"shape": s, "batch": batch, "seq_len": seqlen, "kigalix": k, "llama": l,
                               "kernel_rooflines": rooflines(s, batch, seqlen, k, l, peaks),
                               "attention_kernels": attention_kernels(s, peaks),
+                              "seconds": round(time.time() - t0, 1)}
+    print(json.dumps(out))
+
+
+# ---------------------------------------------------------------------------
+# Pokadra beside Llama
+# ---------------------------------------------------------------------------
+POKADRA_SIZES = {
+    # width, layers (mingru, attention, mingru, attention over layer 1's keys), heads x 2 maps x dim, value size,
+    # key/value heads, window + kept tokens, recurrence width, dense ff, per-token side width
+    "w2048": dict(width=2048, layers=4, heads=16, kv_heads=4, dim=64, vdim=128, window=512, keep=4, gru=2560,
+                  ff=5632, side=64, buckets=100003, vocab=32000),
+    "w4096": dict(width=4096, layers=4, heads=32, kv_heads=8, dim=64, vdim=128, window=512, keep=4, gru=5120,
+                  ff=11008, side=64, buckets=100003, vocab=32000),
+}
+POKADRA_KERNELS = ["bigram_embed", "postnorm_residual", "group_rms_norm", "glu_clamped", "token_gated_gelu",
+                   "mingru_scan", "diff_attn_prepare", "diff_attn"]
+
+
+def pokadra_config(s: dict) -> dict:
+    at = lambda src: {"type": "attention", "mixer": dict(
+        {"heads": s["heads"], "kv_heads": s["kv_heads"], "dim": s["dim"], "vdim": s["vdim"], "diff": 0.5,
+         "scale": s["dim"] ** -0.5, "mask": {"size": s["window"], "keep_first": s["keep"]},
+         "rot": {"base": 10000.0, "dims": s["dim"] // 2,
+                 "scaling": {"factor": 8.0, "original": 4096, "fast": 32.0, "slow": 1.0}}},
+        **({"kv_from": src} if src is not None else {}))}
+    gru = {"type": "mingru", "mixer": {"width": s["gru"]}}
+    mlp = {"kind": "dense", "ff": s["ff"], "limit": 7.0}
+    pattern = [gru, at(None), gru, at(1)]
+    layers = []
+    for i in range(s["layers"]):
+        L = dict(pattern[i % 4], mlp=mlp)
+        if i % 4 == 3:      # the sharing layer reads the cache of the attention layer two places before it
+            L = dict(at(i - 2), mlp=mlp)
+        layers.append(L)
+    return {"architecture": "Pokadra", "width": s["width"], "vocab": s["vocab"], "norm": {"eps": 1e-5, "groups": 4},
+            "residual_mult": 0.5, "token_side": {"dim": s["side"]},
+            "embedding": {"scale": 2.0, "bigram": {"buckets": s["buckets"], "mul_prev": 1000003, "mul_cur": 31}},
+            "layers": layers}
+
+
+def _visible_pairs(ctx: int, q_len: int, window: int, keep: int) -> int:
+    """(query, key) pairs of one sequence with ctx tokens in all whose last q_len are the step's rows."""
+    n = 0
+    for i in range(ctx - q_len, ctx):
+        lo = max(0, i - window + 1) if window else 0
+        n += min(keep, lo) + (i - lo + 1)
+    return n
+
+
+def _frac(ms, nbytes, flops, hbm, tf):
+    t = ms * 1e-3
+    if t <= 0:
+        return None
+    roof = max(nbytes / hbm, flops / tf)
+    return {"ms": ms, "GB": nbytes / 1e9, "TFLOP": flops / 1e12, "of_copy_peak": nbytes / t / hbm,
+            "of_gemm_peak": flops / t / tf, "roof_ms": roof * 1e3, "of_roof": roof / t}
+
+
+def pokadra_rooflines(s: dict, batch: int, seqlen: int, k: dict, l: dict, peaks: dict) -> dict:
+    """Achieved fraction of the nearer roof per kind of kernel, from the per-kernel times of one step of each
+    model (all layers of that kind together)."""
+    hbm, tf = peaks["hbm_gbs"] * 1e9, peaks["bf16_tflops"] * 1e12
+    n_at = sum(1 for i in range(s["layers"]) if i % 2 == 1)
+    n_gru = s["layers"] - n_at
+    H, G, dim, vd, W = s["heads"], s["kv_heads"], s["dim"], s["vdim"], s["width"]
+    out = {}
+    for phase in ("decode", "prefill"):
+        q_len = 1 if phase == "decode" else seqlen
+        ctx = seqlen + 1 if phase == "decode" else seqlen
+        rows = batch * q_len
+        pairs = batch * _visible_pairs(ctx, q_len, s["window"], s["keep"])
+        touched = batch * (min(ctx, s["window"] + s["keep"]) if phase == "decode" else ctx)
+        km, lm = k[phase]["kernels_ms"], l[phase]["kernels_ms"]
+        out[f"pokadra diff_attn {phase}"] = _frac(
+            km.get("diff_attn", 0.0), n_at * (touched * G * (2 * dim + vd) * 2 + rows * H * (2 * dim * 4 + vd * 2)),
+            n_at * pairs * H * 4 * (dim + vd), hbm, tf)
+        Hl, Hkv = W // 128, max(1, W // 512)
+        lpairs = batch * _visible_pairs(ctx, q_len, 0, 0)
+        out[f"llama paged attention {phase}"] = _frac(
+            lm.get("paged_kv_varlen_mha", 0.0), s["layers"] * (batch * ctx * 2 * Hkv * 128 * 2 + rows * Hl * 128 * 4),
+            s["layers"] * lpairs * Hl * 4 * 128, hbm, tf)
+        out[f"pokadra mingru_scan {phase}"] = _frac(km.get("mingru_scan", 0.0), n_gru * rows * s["gru"] * 4 * 2, 0, hbm, tf)
+        n_post = s["layers"] * 3
+        out[f"pokadra postnorm_residual {phase}"] = _frac(
+            km.get("postnorm_residual", 0.0),
+            rows * W * (n_post * (4 + 4 + 2 + 2) + sum(4 * (i + 2) for i in range(s["layers"]))), 0, hbm, tf)
+        out[f"llama rms_norm_residual {phase}"] = _frac(
+            lm.get("rms_norm_residual", 0.0) + lm.get("rms_norm", 0.0), rows * W * (2 * s["layers"] + 1) * 4 * 2, 0, hbm, tf)
+        pw = (n_gru * 4 * s["gru"] * W + n_at * ((2 * H * dim + H * vd + H) * W) + (G * (2 * dim + vd)) * W * (n_at + 1) // 2
+              + s["layers"] * (3 * s["ff"] * W + 2 * s["side"] * W))
+        nlog = batch
+        out[f"pokadra dense GEMMs {phase}"] = _frac(km.get("linear (dense GEMMs)", 0.0), (pw + s["vocab"] * W) * 2,
+                                                   2 * pw * rows + nlog * 2 * s["vocab"] * W, hbm, tf)
+        lw = s["layers"] * (W * (W + 2 * Hkv * 128) + W * W + 3 * s["ff"] * W)
+        out[f"llama dense GEMMs {phase}"] = _frac(lm.get("linear (dense GEMMs)", 0.0), (lw + s["vocab"] * W) * 2,
+                                                 2 * lw * rows + nlog * 2 * s["vocab"] * W, hbm, tf)
+    return out
+
+
+def pokadra_attention_kernels(s: dict, peaks: dict, cases=((64, 4096, 1), (4, 2048, 2048))) -> dict:
+    """The differential attention kernel and the Llama paged attention alone, on caches larger than L2: (batch,
+    cached length, new tokens per sequence) = decoding over long contexts and one prompt portion.  CUDA events
+    around 10 launches after 3."""
+    from . import kernels
+    from .decode_step import BlockPool, StepBuffers, build_step_batch
+    dev = torch.device("cuda", torch.cuda.current_device())
+    hbm, tf = peaks["hbm_gbs"] * 1e9, peaks["bf16_tflops"] * 1e12
+    H, G, dim, vd, win, keep = s["heads"], s["kv_heads"], s["dim"], s["vdim"], s["window"], s["keep"]
+    Hl, Hkv, D, bs = s["width"] // 128, max(1, s["width"] // 512), 128, 16
+    out = {}
+    for batch, ctx, q_len in cases:
+        n_blocks = batch * (-(-ctx // bs)) + 8
+        pool = BlockPool(n_blocks, bs, seed=1)
+        seqs = []
+        for _ in range(batch):
+            sq = pool.open_sequence()
+            pool.reserve(sq, ctx)
+            seqs.append(sq)
+        hb = build_step_batch(pool, seqs, [[0] * q_len] * batch, [ctx - q_len] * batch, list(range(batch)))
+        tokens, positions, prm = StepBuffers(dev, batch * q_len, batch, n_blocks).upload(hb)
+        rows = batch * q_len
+        g = torch.Generator(device=dev).manual_seed(0)
+        rnd = lambda *shape: torch.randn(shape, generator=g, device=dev, dtype=torch.float32).to(torch.bfloat16)
+        kc, vc = rnd(n_blocks * bs, G, 2 * dim), rnd(n_blocks * bs, G, vd)
+        q = torch.randn((rows, H, 2, dim), generator=g, device=dev, dtype=torch.float32)
+        gate = rnd(rows, H)
+        f_diff = lambda: kernels.diff_attn(q, kc, vc, gate, prm.q_cu_seq_lens, prm.kv_cu_seq_lens, prm.block_tables,
+                                           prm.cu_block_lens, prm.token_seq, bs, dim ** -0.5, win, keep, 0.4, 0.5, 1e-5)
+        kl, vl = rnd(n_blocks * bs, Hkv, D), rnd(n_blocks * bs, Hkv, D)
+        ql, ol = rnd(rows, Hl, D), torch.empty((rows, Hl, D), dtype=torch.bfloat16, device=dev)
+        f_llama = lambda: kernels.paged_kv_varlen_mha(ol, ql, kl, vl, prm.q_cu_seq_lens, prm.kv_cu_seq_lens,
+                                                      prm.block_tables, prm.cu_block_lens, None, bs, q_len, ctx,
+                                                      D ** -0.5, 0.0, -1)
+        pairs = batch * _visible_pairs(ctx, q_len, win, keep)
+        touched = batch * (min(ctx, win + keep) if q_len == 1 else ctx)
+        lpairs = batch * _visible_pairs(ctx, q_len, 0, 0)
+        for name, fn, nbytes, flops in (
+                ("pokadra diff_attn", f_diff, touched * G * (2 * dim + vd) * 2 + rows * H * (2 * dim * 4 + vd * 2),
+                 pairs * H * 4 * (dim + vd)),
+                ("llama paged attention", f_llama, batch * ctx * 2 * Hkv * D * 2 + rows * Hl * D * 4, lpairs * Hl * 4 * D)):
+            ms = _time_steps(fn, 3, 10)
+            out[f"{name}, {batch} x {ctx} cached, {q_len} new"] = _frac(ms, nbytes, flops, hbm, tf)
+        del kc, vc, kl, vl
+        torch.cuda.empty_cache()
+    return out
+
+
+def run_pokadra(args) -> None:
+    torch.cuda.set_device(0)
+    torch.backends.cuda.matmul.allow_tf32 = False
+    peaks_path = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "MEASURED_PEAKS.json")
+    peaks = json.load(open(peaks_path)) if os.path.exists(peaks_path) else {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
+    out = {"metric": "pokadra_vs_llama_tokens_per_s", "unit": "tokens/s", "dtype": "bf16",
+           "data": "synthetic (random-init weights, random token ids)", "n_gpus": 1,
+           "peaks": {"hbm_gbs": peaks["hbm_gbs"], "bf16_tflops": peaks["bf16_tflops"],
+                     "source": "measured" if os.path.exists(peaks_path) else "fallback"}, "sizes": {}}
+    names = [args.arch_size] if args.arch_size != "all" else list(POKADRA_SIZES)
+    for name in names:
+        s = POKADRA_SIZES[name]
+        batch, seqlen = args.arch_batch, args.arch_seqlen
+        t0 = time.time()
+        k = _run_model(pokadra_config(s), batch, seqlen, args.warmup, args.steps, POKADRA_KERNELS)
+        l = _run_model(llama_config(s), batch, seqlen, args.warmup, args.steps, LLAMA_KERNELS)
+        out["sizes"][name] = {"shape": s, "batch": batch, "seq_len": seqlen, "pokadra": k, "llama": l,
+                              "kernel_rooflines": pokadra_rooflines(s, batch, seqlen, k, l, peaks),
+                              "attention_kernels": pokadra_attention_kernels(s, peaks),
                               "seconds": round(time.time() - t0, 1)}
     print(json.dumps(out))

@@ -12,17 +12,19 @@
 //
 //   prepare : q rows -> fp32 [rows, H, 2, dim]; k rows -> K cache [slots, G, 2 * dim]; v rows -> V cache
 //             [slots, G, vdim] (cache entries have the activation type T)
-//   attend  : one CTA per (row, head); every warp walks its share of the visible keys in groups of 32 (lane =
-//             key for the two scores, lane = value channel for the weighted sum) with a running maximum and sum
-//             per map; the warps' partial results are merged through shared memory.
+//   attend  : one CTA per (row, key/value head): its warps are the group's query heads times a split of the
+//             visible keys; a warp walks its keys in groups of 32 (lane = key for the two scores, lane = value
+//             channels for the weighted sum) with a running maximum and sum per map, and the splits of a head are
+//             merged through shared memory.
 // Scores, softmax weights, sums, the norm and the gate are fp32.
 #include "common.cuh"
 
 namespace b200 {
 namespace {
 
-constexpr int kWarps = 4;
-constexpr int kMaxVPerLane = 8;      // vdim <= 256
+constexpr int kWarps = 4;           // the per-token kernel
+constexpr int kMaxWarps = 8;        // the attention kernel: heads of a group x key splits
+constexpr int kMaxVdim = 512;
 
 template <typename T>
 __device__ __forceinline__ void norm_rotate_unit(const T* __restrict__ src, const float* __restrict__ w,
@@ -85,37 +87,71 @@ diff_attn_prepare_kernel(float* __restrict__ q_out, const T* __restrict__ q_in, 
   }
 }
 
+// 4 consecutive elements of a cache row as floats (one 8- or 16-byte load)
 template <typename T>
-__global__ void __launch_bounds__(kWarps * 32)
+__device__ __forceinline__ void load4(const T* p, float (&v)[4]);
+template <>
+__device__ __forceinline__ void load4<float>(const float* p, float (&v)[4]) {
+  const float4 x = *reinterpret_cast<const float4*>(p);
+  v[0] = x.x; v[1] = x.y; v[2] = x.z; v[3] = x.w;
+}
+template <>
+__device__ __forceinline__ void load4<__nv_bfloat16>(const __nv_bfloat16* p, float (&v)[4]) {
+  const uint2 x = *reinterpret_cast<const uint2*>(p);
+  const float2 a = Num<__nv_bfloat16>::unpack(x.x), b = Num<__nv_bfloat16>::unpack(x.y);
+  v[0] = a.x; v[1] = a.y; v[2] = b.x; v[3] = b.y;
+}
+template <>
+__device__ __forceinline__ void load4<__half>(const __half* p, float (&v)[4]) {
+  const uint2 x = *reinterpret_cast<const uint2*>(p);
+  const float2 a = Num<__half>::unpack(x.x), b = Num<__half>::unpack(x.y);
+  v[0] = a.x; v[1] = a.y; v[2] = b.x; v[3] = b.y;
+}
+
+// One CTA per (row, key/value head, chunk of RH query heads of that group); warp = (head r, key split s), so the
+// RH heads' reads of the same cache rows meet in L1.  NCH: value channels per lane = 4 * NCH (lane owns channels
+// (c * 32 + lane) * 4 .. + 3 when VEC, lane + 32 * c otherwise).  VEC needs dim % 4 == 0 and vdim % 4 == 0 with
+// 16-byte aligned map starts.
+template <typename T, int NCH, bool VEC>
+__global__ void __launch_bounds__(kMaxWarps * 32)
 diff_attn_kernel(T* __restrict__ out, int64_t ldo, const float* __restrict__ q, const T* __restrict__ k_cache,
                  const T* __restrict__ v_cache, const T* __restrict__ gate, int64_t ldg,
                  const int* __restrict__ q_cu, const int* __restrict__ kv_cu, const int* __restrict__ block_tables,
                  const int* __restrict__ cu_block_lens, const int* __restrict__ token_seq, int H, int G, int dim,
                  int vdim, int block_size, float scale, int window, int keep_first, float lambda, float out_scale,
-                 float eps) {
-  extern __shared__ float sm[];
-  float* q_s = sm;                                   // [2 * dim]
-  float* acc_s = q_s + 2 * dim;                      // [kWarps][2][vdim]
-  float* ml_s = acc_s + kWarps * 2 * vdim;           // [kWarps][4]  m1 l1 m2 l2
-  __shared__ float red[32];
-  const int row = blockIdx.x, h = blockIdx.y, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+                 float eps, int RH, int S) {
+  extern __shared__ __align__(16) float sm[];
+  const int n_warps = RH * S;
+  float* q_s = sm;                                   // [RH][2 * dim]
+  float* acc_s = q_s + RH * 2 * dim;                 // [n_warps][2][vdim]
+  float* ml_s = acc_s + n_warps * 2 * vdim;          // [n_warps][4]  m1 l1 m2 l2
+  const int row = blockIdx.x, g = blockIdx.y, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int R = H / G;
+  const int r = warp % RH, sp = warp / RH;
+  const int h_local = blockIdx.z * RH + r;           // head within the group
+  const bool head_ok = h_local < R;
+  const int h = g * R + (head_ok ? h_local : 0);
   const int seq = token_seq[row];
   const int kv_len = kv_cu[seq + 1] - kv_cu[seq], q_len = q_cu[seq + 1] - q_cu[seq];
   const int i = kv_len - q_len + (row - q_cu[seq]);            // position of this row
-  const int g = h / (H / G);
   const int* table = block_tables + cu_block_lens[seq];
-  for (int d = threadIdx.x; d < 2 * dim; d += kWarps * 32) q_s[d] = q[((size_t)row * H + h) * 2 * dim + d];
+  for (int d = threadIdx.x; d < RH * 2 * dim; d += blockDim.x) {
+    const int rr = d / (2 * dim), hh = blockIdx.z * RH + rr;
+    q_s[d] = hh < R ? q[((size_t)row * H + g * R + hh) * 2 * dim + (d - rr * 2 * dim)] : 0.0f;
+  }
   __syncthreads();
+  const float* q1 = q_s + r * 2 * dim;
+  const float* q2 = q1 + dim;
   // visible keys: the kept first tokens that have left the window, then the window
   const int lo = (window > 0 && i - window + 1 > 0) ? i - window + 1 : 0;
   const int ns = keep_first < lo ? keep_first : lo;
   const int total = ns + (i - lo + 1);
   const size_t k_stride = (size_t)G * 2 * dim, v_stride = (size_t)G * vdim;
   float m1 = -INFINITY, l1 = 0.0f, m2 = -INFINITY, l2 = 0.0f;
-  float a1[kMaxVPerLane], a2[kMaxVPerLane];
+  float a1[4 * NCH], a2[4 * NCH];
 #pragma unroll
-  for (int c = 0; c < kMaxVPerLane; ++c) a1[c] = a2[c] = 0.0f;
-  for (int n0 = warp * 32; n0 < total; n0 += kWarps * 32) {
+  for (int c = 0; c < 4 * NCH; ++c) a1[c] = a2[c] = 0.0f;
+  for (int n0 = sp * 32; n0 < total; n0 += S * 32) {
     const int n = n0 + lane;
     const bool live = n < total;
     int slot = 0;
@@ -125,9 +161,20 @@ diff_attn_kernel(T* __restrict__ out, int64_t ldo, const float* __restrict__ q, 
       slot = table[j / block_size] + j % block_size;
       const T* kr = k_cache + (size_t)slot * k_stride + (size_t)g * 2 * dim;
       float d1 = 0.0f, d2 = 0.0f;
-      for (int d = 0; d < dim; ++d) {
-        d1 += q_s[d] * Num<T>::to_f(kr[d]);
-        d2 += q_s[dim + d] * Num<T>::to_f(kr[dim + d]);
+      if (VEC) {
+        for (int d = 0; d < dim; d += 4) {
+          float x[4], y[4];
+          load4<T>(kr + d, x);
+          load4<T>(kr + dim + d, y);
+          const float4 u = *reinterpret_cast<const float4*>(q1 + d), w = *reinterpret_cast<const float4*>(q2 + d);
+          d1 += u.x * x[0]; d1 += u.y * x[1]; d1 += u.z * x[2]; d1 += u.w * x[3];
+          d2 += w.x * y[0]; d2 += w.y * y[1]; d2 += w.z * y[2]; d2 += w.w * y[3];
+        }
+      } else {
+        for (int d = 0; d < dim; ++d) {
+          d1 += q1[d] * Num<T>::to_f(kr[d]);
+          d2 += q2[d] * Num<T>::to_f(kr[dim + d]);
+        }
       }
       s1 = d1 * scale;
       s2 = d2 * scale;
@@ -146,70 +193,336 @@ diff_attn_kernel(T* __restrict__ out, int64_t ldo, const float* __restrict__ q, 
     m1 = nm1;
     m2 = nm2;
 #pragma unroll
-    for (int c = 0; c < kMaxVPerLane; ++c) { a1[c] *= c1; a2[c] *= c2; }
+    for (int c = 0; c < 4 * NCH; ++c) { a1[c] *= c1; a2[c] *= c2; }
     const int cnt = total - n0 < 32 ? total - n0 : 32;
     for (int kk = 0; kk < cnt; ++kk) {
       const float w1 = __shfl_sync(0xffffffffu, p1, kk), w2 = __shfl_sync(0xffffffffu, p2, kk);
       const int sl = __shfl_sync(0xffffffffu, slot, kk);
       const T* vr = v_cache + (size_t)sl * v_stride + (size_t)g * vdim;
 #pragma unroll
-      for (int c = 0; c < kMaxVPerLane; ++c) {
-        const int col = lane + 32 * c;
-        if (col < vdim) {
-          const float v = Num<T>::to_f(vr[col]);
-          a1[c] += w1 * v;
-          a2[c] += w2 * v;
+      for (int c = 0; c < NCH; ++c) {
+        if (VEC) {
+          const int col = (c * 32 + lane) * 4;
+          if (col < vdim) {
+            float v[4];
+            load4<T>(vr + col, v);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) { a1[c * 4 + e] += w1 * v[e]; a2[c * 4 + e] += w2 * v[e]; }
+          }
+        } else {
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const int col = lane + 32 * (c * 4 + e);
+            if (col < vdim) {
+              const float v = Num<T>::to_f(vr[col]);
+              a1[c * 4 + e] += w1 * v;
+              a2[c * 4 + e] += w2 * v;
+            }
+          }
         }
       }
     }
   }
-  // merge the warps
+  // merge the key splits of every head
   if (lane == 0) {
     ml_s[warp * 4 + 0] = m1; ml_s[warp * 4 + 1] = l1; ml_s[warp * 4 + 2] = m2; ml_s[warp * 4 + 3] = l2;
   }
+  auto col_of = [&](int c, int e) { return VEC ? (c * 32 + lane) * 4 + e : lane + 32 * (c * 4 + e); };
 #pragma unroll
-  for (int c = 0; c < kMaxVPerLane; ++c) {
-    const int col = lane + 32 * c;
-    if (col < vdim) {
-      acc_s[(warp * 2 + 0) * vdim + col] = a1[c];
-      acc_s[(warp * 2 + 1) * vdim + col] = a2[c];
+  for (int c = 0; c < NCH; ++c)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const int col = col_of(c, e);
+      if (col < vdim) {
+        acc_s[(warp * 2 + 0) * vdim + col] = a1[c * 4 + e];
+        acc_s[(warp * 2 + 1) * vdim + col] = a2[c * 4 + e];
+      }
     }
-  }
   __syncthreads();
+  if (sp != 0 || !head_ok) return;
   float M1 = -INFINITY, M2 = -INFINITY;
-#pragma unroll
-  for (int w = 0; w < kWarps; ++w) { M1 = fmaxf(M1, ml_s[w * 4]); M2 = fmaxf(M2, ml_s[w * 4 + 2]); }
-  float L1 = 0.0f, L2 = 0.0f, f1[kWarps], f2[kWarps];
-#pragma unroll
-  for (int w = 0; w < kWarps; ++w) {
-    f1[w] = ml_s[w * 4 + 1] > 0.0f ? expf(ml_s[w * 4] - M1) : 0.0f;
-    f2[w] = ml_s[w * 4 + 3] > 0.0f ? expf(ml_s[w * 4 + 2] - M2) : 0.0f;
-    L1 += f1[w] * ml_s[w * 4 + 1];
-    L2 += f2[w] * ml_s[w * 4 + 3];
+  for (int s2i = 0; s2i < S; ++s2i) {
+    const int w = r + s2i * RH;
+    M1 = fmaxf(M1, ml_s[w * 4]);
+    M2 = fmaxf(M2, ml_s[w * 4 + 2]);
   }
-  float o[2] = {0.0f, 0.0f};       // up to two value channels per thread (vdim <= 256, 128 threads)
+  float L1 = 0.0f, L2 = 0.0f;
+  float o[4 * NCH];
+#pragma unroll
+  for (int c = 0; c < 4 * NCH; ++c) o[c] = 0.0f;
+  float x2[4 * NCH];
+#pragma unroll
+  for (int c = 0; c < 4 * NCH; ++c) x2[c] = 0.0f;
+  for (int s2i = 0; s2i < S; ++s2i) {
+    const int w = r + s2i * RH;
+    const float f1 = ml_s[w * 4 + 1] > 0.0f ? expf(ml_s[w * 4] - M1) : 0.0f;
+    const float f2 = ml_s[w * 4 + 3] > 0.0f ? expf(ml_s[w * 4 + 2] - M2) : 0.0f;
+    L1 += f1 * ml_s[w * 4 + 1];
+    L2 += f2 * ml_s[w * 4 + 3];
+#pragma unroll
+    for (int c = 0; c < NCH; ++c)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int col = col_of(c, e);
+        if (col < vdim) {
+          o[c * 4 + e] += f1 * acc_s[(w * 2 + 0) * vdim + col];
+          x2[c * 4 + e] += f2 * acc_s[(w * 2 + 1) * vdim + col];
+        }
+      }
+  }
   float ss = 0.0f;
 #pragma unroll
-  for (int r = 0; r < 2; ++r) {
-    const int col = threadIdx.x + r * kWarps * 32;
-    if (col < vdim) {
-      float x1 = 0.0f, x2 = 0.0f;
+  for (int c = 0; c < NCH; ++c)
 #pragma unroll
-      for (int w = 0; w < kWarps; ++w) {
-        x1 += f1[w] * acc_s[(w * 2 + 0) * vdim + col];
-        x2 += f2[w] * acc_s[(w * 2 + 1) * vdim + col];
+    for (int e = 0; e < 4; ++e) {
+      if (col_of(c, e) < vdim) {
+        o[c * 4 + e] = o[c * 4 + e] / L1 - lambda * (x2[c * 4 + e] / L2);
+        ss += o[c * 4 + e] * o[c * 4 + e];
       }
-      o[r] = x1 / L1 - lambda * (x2 / L2);
-      ss += o[r] * o[r];
     }
-  }
-  ss = block_sum<kWarps * 32>(ss, red);
+  ss = warp_sum(ss);
   const float gl = gate ? 1.0f / (1.0f + expf(-Num<T>::to_f(gate[(size_t)row * ldg + h]))) : 1.0f;
   const float f = out_scale * gl / sqrtf(ss / (float)vdim + eps);
 #pragma unroll
-  for (int r = 0; r < 2; ++r) {
-    const int col = threadIdx.x + r * kWarps * 32;
-    if (col < vdim) out[(size_t)row * ldo + (size_t)h * vdim + col] = Num<T>::from_f(o[r] * f);
+  for (int c = 0; c < NCH; ++c)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const int col = col_of(c, e);
+      if (col < vdim) out[(size_t)row * ldo + (size_t)h * vdim + col] = Num<T>::from_f(o[c * 4 + e] * f);
+    }
+}
+
+// ------------------------------------------------------------------------------------------------------------
+// Prompt portions in bf16 on the tensor cores (mma.sync m16n8k16, fp32 accumulation).
+// One CTA = 4 warps = RW query heads of one key/value group x (4 / RW) sub-tiles of 16 consecutive tokens of one
+// sequence, so that all warps walk the same key tiles: 32 keys per tile, K [32][2 dim] and V [32][vdim] copied
+// asynchronously (two buffers) through the block table.  Per warp and tile: S1 = Q1 K1^T, S2 = Q2 K2^T, the
+// visibility test per element, a running maximum / sum per row and map in fp32, and O1 += P1 V, O2 += P2 V with
+// the weights entering the product as two bf16 terms (p = hi + lo, 16 mantissa bits).  The tiles visited are those
+// that hold kept first tokens and those of the window of the CTA's tokens.
+// ------------------------------------------------------------------------------------------------------------
+constexpr int kBK = 32;
+
+__device__ __forceinline__ void cp_async16(void* smem_dst, const void* gsrc, bool valid) {
+  const uint32_t d = smem_u32(smem_dst);
+  const int n = valid ? 16 : 0;
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d), "l"(gsrc), "r"(n) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
+__device__ __forceinline__ void ldsm_x4(uint32_t (&r)[4], const void* p) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_u32(p)));
+}
+__device__ __forceinline__ void ldsm_x4_t(uint32_t (&r)[4], const void* p) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_u32(p)));
+}
+__device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void split_bf16(float x, float y, uint32_t& hi, uint32_t& lo) {
+  const __nv_bfloat16 xh = __float2bfloat16_rn(x), yh = __float2bfloat16_rn(y);
+  hi = Num<__nv_bfloat16>::pack(__bfloat162float(xh), __bfloat162float(yh));
+  lo = Num<__nv_bfloat16>::pack(x - __bfloat162float(xh), y - __bfloat162float(yh));
+}
+
+template <int KS_MAX, int VT_MAX>      // dim <= 16 KS_MAX, vdim <= 16 VT_MAX, both multiples of 16
+__global__ void __launch_bounds__(128)
+diff_attn_prefill_kernel(__nv_bfloat16* __restrict__ out, int64_t ldo, const float* __restrict__ q,
+                         const __nv_bfloat16* __restrict__ k_cache, const __nv_bfloat16* __restrict__ v_cache,
+                         const __nv_bfloat16* __restrict__ gate, int64_t ldg, const int* __restrict__ q_cu,
+                         const int* __restrict__ kv_cu, const int* __restrict__ block_tables,
+                         const int* __restrict__ cu_block_lens, int H, int G, int dim, int vdim, int block_size,
+                         float scale, int window, int keep_first, float lambda, float out_scale, float eps, int RW,
+                         int chunks) {
+  extern __shared__ __align__(16) unsigned char smraw[];
+  const int KROW = 2 * dim + 8, VROW = vdim + 8;        // bf16 elements per staged row (16 bytes of padding)
+  __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(smraw);     // [4][16][KROW]
+  __nv_bfloat16* Ks = Qs + 4 * 16 * KROW;                          // [2][kBK][KROW]
+  __nv_bfloat16* Vs = Ks + 2 * kBK * KROW;                         // [2][kBK][VROW]
+  const int seq = blockIdx.y, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = blockIdx.z / chunks, chunk = blockIdx.z % chunks;
+  const int R = H / G, TW = 4 / RW, BQ = 16 * TW;
+  const int q0 = q_cu[seq], q_len = q_cu[seq + 1] - q0, kv_len = kv_cu[seq + 1] - kv_cu[seq];
+  const int t0 = blockIdx.x * BQ;                      // first token of the CTA within the step's portion
+  if (t0 >= q_len) return;
+  const int first_pos = kv_len - q_len;
+  const int hr = warp % RW, ts = warp / RW;
+  const int h_local = chunk * RW + hr;
+  const bool head_ok = h_local < R;
+  const int h = g * R + (head_ok ? h_local : 0);
+  const int KS = dim / 16, VT = vdim / 16;
+  const int* table = block_tables + cu_block_lens[seq];
+  // stage this warp's 16 query rows (both maps) as bf16
+  {
+    __nv_bfloat16* qw = Qs + warp * 16 * KROW;
+    for (int e = lane; e < 16 * 2 * dim; e += 32) {
+      const int rr = e / (2 * dim), d = e - rr * 2 * dim;
+      const int t = t0 + ts * 16 + rr;
+      const float v = (t < q_len && head_ok) ? q[((size_t)(q0 + t) * H + h) * 2 * dim + d] : 0.0f;
+      qw[rr * KROW + d] = __float2bfloat16_rn(v);
+    }
+  }
+  // key tiles of the CTA: positions P0 .. P1 of its tokens
+  const int P0 = first_pos + t0;
+  const int P1 = first_pos + (t0 + BQ < q_len ? t0 + BQ : q_len) - 1;
+  const int lo = (window > 0 && P0 - window + 1 > 0) ? P0 - window + 1 : 0;
+  const int ns = keep_first < lo ? keep_first : lo;
+  const int sink_tiles = (ns + kBK - 1) / kBK;
+  const int wt0 = lo / kBK > sink_tiles ? lo / kBK : sink_tiles;
+  const int n_tiles = sink_tiles + (P1 / kBK - wt0 + 1);
+  auto tile_j0 = [&](int idx) { return (idx < sink_tiles ? idx : wt0 + idx - sink_tiles) * kBK; };
+  const size_t k_stride = (size_t)G * 2 * dim, v_stride = (size_t)G * vdim;
+  auto load_tile = [&](int idx, int buf) {
+    const int j0 = tile_j0(idx);
+    const int key = threadIdx.x >> 2, sub = threadIdx.x & 3;
+    const int j = j0 + key;
+    const bool ok = j <= P1;
+    size_t slot = 0;
+    if (ok) slot = (size_t)table[j / block_size] + j % block_size;
+    const __nv_bfloat16* kr = k_cache + slot * k_stride + (size_t)g * 2 * dim;
+    const __nv_bfloat16* vr = v_cache + slot * v_stride + (size_t)g * vdim;
+    __nv_bfloat16* kd = Ks + ((size_t)buf * kBK + key) * KROW;
+    __nv_bfloat16* vd = Vs + ((size_t)buf * kBK + key) * VROW;
+    for (int c = sub; c < dim / 4; c += 4) cp_async16(kd + c * 8, kr + c * 8, ok);
+    for (int c = sub; c < vdim / 8; c += 4) cp_async16(vd + c * 8, vr + c * 8, ok);
+  };
+  load_tile(0, 0);
+  cp_async_commit();
+
+  const int gr = lane >> 2, qc = (lane & 3) * 2;      // fragment row within 8, first column of the pair
+  const int row_t[2] = {t0 + ts * 16 + gr, t0 + ts * 16 + gr + 8};
+  int pos[2];
+#pragma unroll
+  for (int r2 = 0; r2 < 2; ++r2) pos[r2] = (row_t[r2] < q_len && head_ok) ? first_pos + row_t[r2] : -1;
+  float mx[2][2], ls[2][2];                            // [map][row]
+  float o[2][VT_MAX * 2][4];
+#pragma unroll
+  for (int m = 0; m < 2; ++m) {
+    mx[m][0] = mx[m][1] = -INFINITY;
+    ls[m][0] = ls[m][1] = 0.0f;
+#pragma unroll
+    for (int n = 0; n < VT_MAX * 2; ++n) o[m][n][0] = o[m][n][1] = o[m][n][2] = o[m][n][3] = 0.0f;
+  }
+  const __nv_bfloat16* qw = Qs + warp * 16 * KROW;
+  for (int it = 0; it < n_tiles; ++it) {
+    const int buf = it & 1;
+    cp_async_wait_all();
+    __syncthreads();                                   // tile `it` has landed; everyone is done with tile it - 1
+    if (it + 1 < n_tiles) load_tile(it + 1, buf ^ 1);
+    cp_async_commit();
+    const int j0 = tile_j0(it);
+    const __nv_bfloat16* kt = Ks + (size_t)buf * kBK * KROW;
+    const __nv_bfloat16* vt = Vs + (size_t)buf * kBK * VROW;
+#pragma unroll
+    for (int m = 0; m < 2; ++m) {
+      float sc[4][4];
+#pragma unroll
+      for (int n = 0; n < 4; ++n) sc[n][0] = sc[n][1] = sc[n][2] = sc[n][3] = 0.0f;
+#pragma unroll
+      for (int ks = 0; ks < KS_MAX; ++ks) {
+        if (ks < KS) {
+          uint32_t a[4];
+          ldsm_x4(a, qw + (lane & 15) * KROW + m * dim + ks * 16 + (lane >> 4) * 8);
+#pragma unroll
+          for (int np = 0; np < 2; ++np) {             // two n-tiles (16 keys) per load
+            uint32_t b[4];
+            ldsm_x4(b, kt + (np * 16 + (lane & 7) + (lane >> 4) * 8) * KROW + m * dim + ks * 16 + ((lane >> 3) & 1) * 8);
+            mma_bf16(sc[np * 2], a, b[0], b[1]);
+            mma_bf16(sc[np * 2 + 1], a, b[2], b[3]);
+          }
+        }
+      }
+      // visibility, running maximum and sum
+      float rmax[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+      for (int n = 0; n < 4; ++n)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int j = j0 + n * 8 + qc + (e & 1), i = pos[e >> 1];
+          const bool vis = j <= i && (window <= 0 || i - j < window || j < keep_first);
+          const float v = vis ? sc[n][e] * scale : -INFINITY;
+          sc[n][e] = v;
+          rmax[e >> 1] = fmaxf(rmax[e >> 1], v);
+        }
+      float corr[2], msafe[2];
+#pragma unroll
+      for (int r2 = 0; r2 < 2; ++r2) {
+        rmax[r2] = fmaxf(rmax[r2], __shfl_xor_sync(0xffffffffu, rmax[r2], 1));
+        rmax[r2] = fmaxf(rmax[r2], __shfl_xor_sync(0xffffffffu, rmax[r2], 2));
+        const float nm = fmaxf(mx[m][r2], rmax[r2]);
+        msafe[r2] = nm == -INFINITY ? 0.0f : nm;
+        corr[r2] = expf(mx[m][r2] - msafe[r2]);
+        mx[m][r2] = nm;
+        ls[m][r2] *= corr[r2];
+      }
+#pragma unroll
+      for (int n = 0; n < VT_MAX * 2; ++n) {
+        o[m][n][0] *= corr[0]; o[m][n][1] *= corr[0];
+        o[m][n][2] *= corr[1]; o[m][n][3] *= corr[1];
+      }
+      uint32_t phi[2][4], plo[2][4];                   // A fragments of the two 16-key steps
+#pragma unroll
+      for (int n = 0; n < 4; ++n) {
+        const float p0 = expf(sc[n][0] - msafe[0]), p1 = expf(sc[n][1] - msafe[0]);
+        const float p2 = expf(sc[n][2] - msafe[1]), p3 = expf(sc[n][3] - msafe[1]);
+        ls[m][0] += p0 + p1;
+        ls[m][1] += p2 + p3;
+        const int kk = n >> 1, half = (n & 1) * 2;
+        split_bf16(p0, p1, phi[kk][half], plo[kk][half]);
+        split_bf16(p2, p3, phi[kk][half + 1], plo[kk][half + 1]);
+      }
+#pragma unroll
+      for (int kk = 0; kk < 2; ++kk)
+#pragma unroll
+        for (int vt16 = 0; vt16 < VT_MAX; ++vt16) {
+          if (vt16 < VT) {
+            uint32_t b[4];
+            ldsm_x4_t(b, vt + (kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * VROW + vt16 * 16 + (lane >> 4) * 8);
+            mma_bf16(o[m][vt16 * 2], phi[kk], b[0], b[1]);
+            mma_bf16(o[m][vt16 * 2], plo[kk], b[0], b[1]);
+            mma_bf16(o[m][vt16 * 2 + 1], phi[kk], b[2], b[3]);
+            mma_bf16(o[m][vt16 * 2 + 1], plo[kk], b[2], b[3]);
+          }
+        }
+    }
+  }
+  cp_async_wait_all();
+  // rows: sums over the quad, the difference of the maps, the head's root mean square, the gate
+#pragma unroll
+  for (int m = 0; m < 2; ++m)
+#pragma unroll
+    for (int r2 = 0; r2 < 2; ++r2) {
+      ls[m][r2] += __shfl_xor_sync(0xffffffffu, ls[m][r2], 1);
+      ls[m][r2] += __shfl_xor_sync(0xffffffffu, ls[m][r2], 2);
+    }
+  float ss[2] = {0.0f, 0.0f};
+#pragma unroll
+  for (int n = 0; n < VT_MAX * 2; ++n)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const int r2 = e >> 1;
+      const float d = (n < VT * 2) ? o[0][n][e] / ls[0][r2] - lambda * (o[1][n][e] / ls[1][r2]) : 0.0f;
+      o[0][n][e] = d;
+      ss[r2] += d * d;
+    }
+#pragma unroll
+  for (int r2 = 0; r2 < 2; ++r2) {
+    ss[r2] += __shfl_xor_sync(0xffffffffu, ss[r2], 1);
+    ss[r2] += __shfl_xor_sync(0xffffffffu, ss[r2], 2);
+    if (pos[r2] < 0) continue;
+    const size_t row = (size_t)q0 + row_t[r2];
+    const float gl = gate ? 1.0f / (1.0f + expf(-__bfloat162float(gate[row * ldg + h]))) : 1.0f;
+    const float f = out_scale * gl / sqrtf(ss[r2] / (float)vdim + eps);
+    __nv_bfloat16* dst = out + row * ldo + (size_t)h * vdim;
+#pragma unroll
+    for (int n = 0; n < VT_MAX * 2; ++n)
+      if (n < VT * 2)
+        *reinterpret_cast<uint32_t*>(dst + n * 8 + qc) =
+            Num<__nv_bfloat16>::pack(o[0][n][r2 * 2] * f, o[0][n][r2 * 2 + 1] * f);
   }
 }
 
@@ -258,19 +571,41 @@ int b200_diff_attn(void* out, int64_t ldo, const float* q, const void* k_cache, 
   if (rows == 0) return B200_OK;
   B200_CHECK_ARG(out && q && k_cache && v_cache && q_cu_lens && kv_cu_lens && block_tables && cu_block_lens &&
                      token_seq, "diff_attn: null pointer");
-  B200_CHECK_ARG(rows > 0 && H > 0 && H <= 65535 && G > 0 && H % G == 0 && dim > 0 && vdim > 0 &&
-                     vdim <= 32 * kMaxVPerLane && block_size > 0 && ldo >= H * vdim && window >= 0 &&
+  B200_CHECK_ARG(rows > 0 && H > 0 && G > 0 && G <= 65535 && H % G == 0 && dim > 0 && vdim > 0 &&
+                     vdim <= kMaxVdim && block_size > 0 && ldo >= H * vdim && window >= 0 &&
                      window < (1ll << 31) && keep_first >= 0 && keep_first < (1ll << 31),
-                 "diff_attn: bad shape (value width at most 256; window 0 = every earlier key)");
+                 "diff_attn: bad shape (value width at most 512; window 0 = every earlier key)");
   auto st = static_cast<cudaStream_t>(stream);
-  const size_t smem = (size_t)(2 * dim + kWarps * 2 * vdim + kWarps * 4) * sizeof(float);
-  B200_CHECK_ARG(smem <= 48 * 1024, "diff_attn: head too wide");
-  dim3 grid((unsigned)rows, (unsigned)H);
+  const int R = (int)(H / G);
+  const int RH = R < kMaxWarps ? R : kMaxWarps;     // query heads of the group per CTA
+  const int S = kMaxWarps / RH;                     // key splits per head
+  const int chunks = (R + RH - 1) / RH;
+  const size_t smem = (size_t)(RH * 2 * dim + RH * S * 2 * vdim + RH * S * 4) * sizeof(float);
+  B200_CHECK_ARG(smem <= 200 * 1024 && chunks <= 65535, "diff_attn: heads too wide");
+  const int esz = dtype == B200_FP32 ? 4 : 2;
+  const bool vec = dim % 4 == 0 && vdim % 4 == 0 && (dim * esz) % 16 == 0 && (vdim * esz) % 8 == 0 &&
+                   is_aligned(k_cache, 16) && is_aligned(v_cache, 16);
+  const int nch = vdim <= 128 ? 1 : (vdim <= 256 ? 2 : 4);
+  dim3 grid((unsigned)rows, (unsigned)G, (unsigned)chunks);
+#define DA_LAUNCH(T, NCH, VEC)                                                                                 \
+  do {                                                                                                         \
+    if (smem > 48 * 1024)                                                                                      \
+      B200_CUDA_OK(cudaFuncSetAttribute(diff_attn_kernel<T, NCH, VEC>,                                         \
+                                        cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));              \
+    diff_attn_kernel<T, NCH, VEC><<<grid, RH * S * 32, smem, st>>>(                                            \
+        static_cast<T*>(out), ldo, q, static_cast<const T*>(k_cache), static_cast<const T*>(v_cache),         \
+        static_cast<const T*>(gate), ldg, q_cu_lens, kv_cu_lens, block_tables, cu_block_lens, token_seq,      \
+        (int)H, (int)G, (int)dim, (int)vdim, (int)block_size, scale, (int)window, (int)keep_first, lambda,    \
+        out_scale, eps, RH, S);                                                                                \
+  } while (0)
 #define DA_CALL(T)                                                                                             \
-  diff_attn_kernel<T><<<grid, kWarps * 32, smem, st>>>(                                                        \
-      static_cast<T*>(out), ldo, q, static_cast<const T*>(k_cache), static_cast<const T*>(v_cache),           \
-      static_cast<const T*>(gate), ldg, q_cu_lens, kv_cu_lens, block_tables, cu_block_lens, token_seq, (int)H, \
-      (int)G, (int)dim, (int)vdim, (int)block_size, scale, (int)window, (int)keep_first, lambda, out_scale, eps)
+  do {                                                                                                         \
+    if (vec) {                                                                                                 \
+      if (nch == 1) DA_LAUNCH(T, 1, true); else if (nch == 2) DA_LAUNCH(T, 2, true); else DA_LAUNCH(T, 4, true); \
+    } else {                                                                                                   \
+      if (nch == 1) DA_LAUNCH(T, 1, false); else if (nch == 2) DA_LAUNCH(T, 2, false); else DA_LAUNCH(T, 4, false); \
+    }                                                                                                          \
+  } while (0)
   switch (dtype) {
     case B200_BF16: DA_CALL(__nv_bfloat16); break;
     case B200_FP16: DA_CALL(__half); break;
@@ -278,7 +613,60 @@ int b200_diff_attn(void* out, int64_t ldo, const float* q, const void* k_cache, 
     default: return set_error(B200_ERR_INVALID_ARG, "bad dtype %d", dtype);
   }
 #undef DA_CALL
+#undef DA_LAUNCH
   B200_LAUNCH_OK("diff_attn_kernel");
+  return B200_OK;
+}
+
+}  // extern "C"
+
+extern "C" {
+
+int b200_diff_attn_prefill_supported(int64_t dim, int64_t vdim, int dtype) {
+  return dtype == B200_BF16 && dim > 0 && vdim > 0 && dim % 16 == 0 && vdim % 16 == 0 && dim <= 128 && vdim <= 128;
+}
+
+int b200_diff_attn_prefill(void* out, int64_t ldo, const float* q, const void* k_cache, const void* v_cache,
+                           const void* gate, int64_t ldg, const int32_t* q_cu_lens, const int32_t* kv_cu_lens,
+                           const int32_t* block_tables, const int32_t* cu_block_lens, int64_t n_seq, int64_t q_max,
+                           int64_t H, int64_t G, int64_t dim, int64_t vdim, int64_t block_size, float scale,
+                           int64_t window, int64_t keep_first, float lambda, float out_scale, float eps, int dtype,
+                           b200_stream_t stream) {
+  if (n_seq == 0 || q_max == 0) return B200_OK;
+  B200_CHECK_ARG(out && q && k_cache && v_cache && q_cu_lens && kv_cu_lens && block_tables && cu_block_lens,
+                 "diff_attn_prefill: null pointer");
+  if (!b200_diff_attn_prefill_supported(dim, vdim, dtype))
+    return set_error(B200_ERR_UNSUPPORTED, "diff_attn_prefill: bf16 with dim and vdim multiples of 16 up to 128");
+  B200_CHECK_ARG(n_seq > 0 && n_seq <= 65535 && q_max > 0 && H > 0 && G > 0 && H % G == 0 && block_size > 0 &&
+                     ldo >= H * vdim && ldo % 2 == 0 && window >= 0 && window < (1ll << 31) && keep_first >= 0 &&
+                     keep_first < (1ll << 31) && is_aligned(k_cache, 16) && is_aligned(v_cache, 16) &&
+                     is_aligned(out, 4),
+                 "diff_attn_prefill: bad shape or alignment");
+  auto st = static_cast<cudaStream_t>(stream);
+  const int R = (int)(H / G);
+  const int RW = R >= 4 ? 4 : (R >= 2 ? 2 : 1);
+  const int chunks = (R + RW - 1) / RW;
+  const int BQ = 16 * (4 / RW);
+  B200_CHECK_ARG(G * chunks <= 65535, "diff_attn_prefill: too many heads");
+  const size_t smem = ((size_t)(4 * 16 + 2 * kBK) * (2 * dim + 8) + (size_t)2 * kBK * (vdim + 8)) * 2;
+  dim3 grid((unsigned)((q_max + BQ - 1) / BQ), (unsigned)n_seq, (unsigned)(G * chunks));
+#define DAP_LAUNCH(KS, VT)                                                                                     \
+  do {                                                                                                         \
+    if (smem > 48 * 1024)                                                                                      \
+      B200_CUDA_OK(cudaFuncSetAttribute(diff_attn_prefill_kernel<KS, VT>,                                      \
+                                        cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));              \
+    diff_attn_prefill_kernel<KS, VT><<<grid, 128, smem, st>>>(                                                 \
+        static_cast<__nv_bfloat16*>(out), ldo, q, static_cast<const __nv_bfloat16*>(k_cache),                  \
+        static_cast<const __nv_bfloat16*>(v_cache), static_cast<const __nv_bfloat16*>(gate), ldg, q_cu_lens,   \
+        kv_cu_lens, block_tables, cu_block_lens, (int)H, (int)G, (int)dim, (int)vdim, (int)block_size, scale,  \
+        (int)window, (int)keep_first, lambda, out_scale, eps, RW, chunks);                                     \
+  } while (0)
+  if (dim <= 64 && vdim <= 64) DAP_LAUNCH(4, 4);
+  else if (dim <= 64) DAP_LAUNCH(4, 8);
+  else if (vdim <= 64) DAP_LAUNCH(8, 4);
+  else DAP_LAUNCH(8, 8);
+#undef DAP_LAUNCH
+  B200_LAUNCH_OK("diff_attn_prefill_kernel");
   return B200_OK;
 }
 

@@ -993,12 +993,18 @@ def diff_attn_prepare(q_in: torch.Tensor, k_in: Optional[torch.Tensor], v_in: Op
     return q
 
 
+# a step whose longest portion has at least this many tokens runs the tensor-core kernel (bf16, fitting head sizes)
+DIFF_ATTN_PREFILL_MIN_ROWS = 4
+
+
 def diff_attn(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, gate: Optional[torch.Tensor],
               q_cu: torch.Tensor, kv_cu: torch.Tensor, block_tables: torch.Tensor, cu_block_lens: torch.Tensor,
               token_seq: torch.Tensor, block_size: int, scale: float, window: int, keep_first: int, lam: float,
-              out_scale: float, eps: float) -> torch.Tensor:
+              out_scale: float, eps: float, n_seq: int = 0, q_max: int = 0) -> torch.Tensor:
     """[rows, H * vdim] in the cache's dtype: (softmax(s1) V - lam softmax(s2) V), RMS-normalised per head, times
-    out_scale and sigmoid(gate [rows, H])."""
+    out_scale and sigmoid(gate [rows, H]).  With n_seq and q_max (the step's sequence count and longest portion,
+    host numbers) a step with prompt portions in bf16 runs on the tensor cores where the head sizes allow it;
+    otherwise, and for single tokens, fp32 and odd sizes, the CUDA-core kernel runs."""
     _cuda(q, k_cache, v_cache, gate)
     _f32(q)
     _check_i32(q_cu, kv_cu, block_tables, cu_block_lens, token_seq)
@@ -1006,9 +1012,18 @@ def diff_attn(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, gat
     G, vdim = v_cache.shape[1], v_cache.shape[2]
     assert gate is None or (gate.shape == (rows, H) and gate.stride(1) == 1 and gate.dtype == k_cache.dtype)
     out = torch.empty((rows, H * vdim), dtype=k_cache.dtype, device=q.device)
-    check(_lib.load().b200_diff_attn(_p(out), H * vdim, _p(q), _p(k_cache), _p(v_cache), _p(gate),
-                                     gate.stride(0) if gate is not None else 0, _p(q_cu), _p(kv_cu),
-                                     _p(block_tables), _p(cu_block_lens), _p(token_seq), rows, H, G, dim, vdim,
-                                     block_size, scale, window, keep_first, lam, out_scale, eps, _dt(k_cache),
-                                     _stream()))
+    lib = _lib.load()
+    if (n_seq > 0 and q_max >= DIFF_ATTN_PREFILL_MIN_ROWS and os.environ.get("B200_DIFF_ATTN_IMPL") != "simt"
+            and lib.b200_diff_attn_prefill_supported(dim, vdim, _dt(k_cache))):
+        check(lib.b200_diff_attn_prefill(_p(out), H * vdim, _p(q), _p(k_cache), _p(v_cache), _p(gate),
+                                         gate.stride(0) if gate is not None else 0, _p(q_cu), _p(kv_cu),
+                                         _p(block_tables), _p(cu_block_lens), n_seq, q_max, H, G, dim, vdim,
+                                         block_size, scale, window, keep_first, lam, out_scale, eps, _dt(k_cache),
+                                         _stream()))
+        return out
+    check(lib.b200_diff_attn(_p(out), H * vdim, _p(q), _p(k_cache), _p(v_cache), _p(gate),
+                             gate.stride(0) if gate is not None else 0, _p(q_cu), _p(kv_cu),
+                             _p(block_tables), _p(cu_block_lens), _p(token_seq), rows, H, G, dim, vdim,
+                             block_size, scale, window, keep_first, lam, out_scale, eps, _dt(k_cache),
+                             _stream()))
     return out

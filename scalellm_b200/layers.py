@@ -861,7 +861,8 @@ class DiffAttention:
         gate = proj[:, self.v_end: self.v_end + self.H] if self.has_gate else None
         o = kernels.diff_attn(q, cache.key_cache, cache.value_cache, gate, params.q_cu_seq_lens, params.kv_cu_seq_lens,
                               params.block_tables, params.cu_block_lens, params.token_seq, cache.block_size(),
-                              self.scale, self.window, self.keep_first, self.lam, 1.0 - self.diff, self.eps)
+                              self.scale, self.window, self.keep_first, self.lam, 1.0 - self.diff, self.eps,
+                              params.num_sequences, params.q_max_seq_len)
         return self.o_proj(o)
 
     __call__ = forward

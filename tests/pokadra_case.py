@@ -107,18 +107,19 @@ def logits_error(got: torch.Tensor, want: torch.Tensor) -> float:
 # the configurations the model-level tests run: both mixers in several orders, key/value heads shared by 1, 2 and 3
 # query heads, widths that are not powers of two, 1 to 3 norm groups, a layer without feed-forward, layers that
 # attend over an earlier layer's keys (adjacent and not), windows 5 to 24 with 0 to 4 kept tokens, full rotation,
-# partial rotation, none; with and without the pair table and the per-token term
+# partial rotation, none; with and without the pair table and the per-token term; head sizes that fit the
+# tensor-core kernel (multiples of 16) and head sizes that do not
 CONFIGS = {
     "mix": config([(gru(40), dense(80)),
-                   (attn(4, 2, 16, 24, window=9, keep_first=3, rot_dims=8, yarn=True), dense(48, 1.0)),
+                   (attn(4, 2, 16, 32, window=9, keep_first=3, rot_dims=8, yarn=True), dense(48, 1.0)),
                    (gru(72), None),
-                   (attn(4, 2, 16, 24, window=5, keep_first=0, rot_dims=8, yarn=True, kv_from=1, diff=0.3), dense(64)),
+                   (attn(4, 2, 16, 32, window=5, keep_first=0, rot_dims=8, yarn=True, kv_from=1, diff=0.3), dense(64)),
                    (attn(3, 3, 8, 8, window=24, keep_first=4, rot_dims=8), dense(40))],
                   width=64, vocab=97, groups=2),
     "attn_first": config([(attn(6, 2, 12, 20, rot_dims=4, diff=0.8), dense(56, 0.7)),
                           (gru(30), dense(44)),
                           (attn(6, 2, 12, 20, window=7, keep_first=1, rot_dims=4, kv_from=0), None)],
                          width=48, vocab=61, groups=3, eps=1e-6, mult=1.0, scale=1.0, bigram=None, side=4),
-    "plain": config([(attn(2, 1, 32, 40, window=13, keep_first=2), dense(96)), (gru(100), dense(72))],
+    "plain": config([(attn(2, 1, 32, 48, window=13, keep_first=2), dense(96)), (gru(100), dense(72))],
                     width=80, vocab=130, groups=1, mult=0.25, bigram=(17, 3, 1), side=0),
 }

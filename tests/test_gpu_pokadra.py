@@ -188,7 +188,7 @@ def _attend_case(dtype, H, G, dim, vdim, window, keep, block_size, cached, n_new
     lam, diff, scale = 0.45, 0.3, 1.0 / math.sqrt(dim)
     got = kernels.diff_attn(q.to(DEV), kc.to(DEV), vc.to(DEV), gate.to(DEV), par.q_cu_seq_lens, par.kv_cu_seq_lens,
                             par.block_tables, par.cu_block_lens, par.token_seq, block_size, scale, window, keep, lam,
-                            1.0 - diff, 1e-5)
+                            1.0 - diff, 1e-5, 1, n_new)       # prompt-sized bf16 cases take the tensor-core kernel
     mask = {"size": window, "keep_first": keep} if window else None
     want = op.diff_attend(q.double(), K.double(), V.double(), pos, scale, mask, lam, diff, 1e-5)
     want = want * torch.sigmoid(gate.double())[:, :, None]
@@ -196,7 +196,8 @@ def _attend_case(dtype, H, G, dim, vdim, window, keep, block_size, cached, n_new
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("H,G,dim,vdim", [(4, 2, 16, 24), (3, 3, 20, 8), (2, 1, 64, 130)])
+@pytest.mark.parametrize("H,G,dim,vdim", [(4, 2, 16, 24), (3, 3, 20, 8), (2, 1, 64, 130), (8, 2, 48, 80), (2, 2, 64, 128),
+                                          (3, 1, 32, 16), (6, 2, 128, 64), (16, 2, 16, 32)])
 def test_attention_window_and_kept_tokens_edges(dtype, H, G, dim, vdim):
     """Decoded rows (one new token each) and prompt rows whose loud key lies just inside / just outside the window,
     on the last kept token / the first one not kept, and far back with no window at all."""
@@ -222,9 +223,16 @@ def test_attention_first_tokens_and_block_borders(dtype):
     tol = 1e-4 if dtype == torch.float32 else 0.05
     # a prompt from position 0: rows shorter than the window, shorter than the kept tokens, and block size 1 / 3 / 16
     for bs in (1, 3, 16):
-        got, want = _attend_case(dtype, 4, 2, 16, 24, 5, 2, bs, 0, 19, [0, 0, 1, 2, 3, 1, 2, 2, None, 4, 6, 7, 1, 9, 9, None, 0, 13, 18],
-                                 seed=bs)
-        assert float((got - want).abs().max()) < tol
+        for vdim in (24, 32):       # CUDA-core and (bf16) tensor-core kernel
+            got, want = _attend_case(dtype, 4, 2, 16, vdim, 5, 2, bs, 0, 19,
+                                     [0, 0, 1, 2, 3, 1, 2, 2, None, 4, 6, 7, 1, 9, 9, None, 0, 13, 18], seed=bs)
+            assert float((got - want).abs().max()) < tol
+    # long portions on top of a long cache: key tiles that hold kept tokens only, the window's first tile, tile borders
+    for win, kp, cached, n_new in ((40, 35, 100, 70), (33, 0, 31, 97), (0, 0, 64, 64), (64, 70, 200, 33), (200, 3, 5, 130)):
+        loud = [None] * n_new
+        loud[0], loud[-1], loud[n_new // 2] = max(0, cached - win + 1) if win else 0, kp - 1 if kp else cached, 0
+        got, want = _attend_case(dtype, 4, 2, 32, 48, win, kp, 16, cached, n_new, loud, seed=win + kp)
+        assert float((got - want).abs().max()) < tol, (win, kp, cached, n_new)
     # window as long as, and longer than, the sequence; more kept tokens than the sequence has
     for win, kp in ((19, 0), (64, 0), (3, 40)):
         got, want = _attend_case(dtype, 2, 2, 8, 8, win, kp, 4, 0, 19, [None] * 19, seed=win)
