@@ -588,6 +588,15 @@ B200_API int b200_mingru_scan(void* out, int64_t ldo, const void* proj, int64_t 
                               const float* x_bias /*nullable*/, float* state, const int32_t* q_cu_lens,
                               const int32_t* positions, const int32_t* state_slots, int64_t n_seq, int64_t width,
                               int dtype, b200_stream_t stream);
+/* The same scan with every portion cut into chunks of chunk_len tokens that run side by side (two kernels: the
+ * chunks' (A, B) with S_end = A S_start + B, then every chunk from the fold of those before it).  q_max: the longest
+ * portion of the step; workspace: fp32, at least ..._workspace_floats. */
+B200_API int64_t b200_mingru_chunked_workspace_floats(int64_t n_seq, int64_t width, int64_t q_max, int64_t chunk_len);
+B200_API int b200_mingru_scan_chunked(void* out, int64_t ldo, const void* proj, int64_t ld,
+                                      const float* z_bias /*nullable*/, const float* x_bias /*nullable*/, float* state,
+                                      const int32_t* q_cu_lens, const int32_t* positions, const int32_t* state_slots,
+                                      int64_t n_seq, int64_t width, int64_t q_max, int64_t chunk_len, float* workspace,
+                                      int64_t workspace_floats, int dtype, b200_stream_t stream);
 /* Differential attention, per token (see diff_attn.cu): RMS norm + rotation of the H * 2 query maps into q_out
  * (fp32 [rows, H, 2, dim]) and, when k_in is given, of the G * 2 key maps into k_cache[slot] ([slots, G, 2 * dim])
  * with v_in copied to v_cache[slot] ([slots, G, vdim]).  q_in / k_in / v_in: rows of stride ld. */

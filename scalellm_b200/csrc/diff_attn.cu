@@ -23,7 +23,7 @@ namespace b200 {
 namespace {
 
 constexpr int kWarps = 4;           // the per-token kernel
-constexpr int kMaxWarps = 8;        // the attention kernel: heads of a group x key splits
+constexpr int kMaxWarps = 16;       // the attention kernel: heads of a group x key splits
 constexpr int kMaxVdim = 512;
 
 template <typename T>
@@ -154,11 +154,12 @@ diff_attn_kernel(T* __restrict__ out, int64_t ldo, const float* __restrict__ q, 
   for (int n0 = sp * 32; n0 < total; n0 += S * 32) {
     const int n = n0 + lane;
     const bool live = n < total;
-    int slot = 0;
     float s1 = -INFINITY, s2 = -INFINITY;
+    // lanes past the last key point at the row's own position (always written) with weight 0, so that the
+    // weighted sum below runs over all 32 lanes without a test
+    const int j = live ? (n < ns ? n : lo + (n - ns)) : i;
+    const int slot = table[j / block_size] + j % block_size;
     if (live) {
-      const int j = n < ns ? n : lo + (n - ns);
-      slot = table[j / block_size] + j % block_size;
       const T* kr = k_cache + (size_t)slot * k_stride + (size_t)g * 2 * dim;
       float d1 = 0.0f, d2 = 0.0f;
       if (VEC) {
@@ -194,8 +195,8 @@ diff_attn_kernel(T* __restrict__ out, int64_t ldo, const float* __restrict__ q, 
     m2 = nm2;
 #pragma unroll
     for (int c = 0; c < 4 * NCH; ++c) { a1[c] *= c1; a2[c] *= c2; }
-    const int cnt = total - n0 < 32 ? total - n0 : 32;
-    for (int kk = 0; kk < cnt; ++kk) {
+#pragma unroll 8
+    for (int kk = 0; kk < 32; ++kk) {
       const float w1 = __shfl_sync(0xffffffffu, p1, kk), w2 = __shfl_sync(0xffffffffu, p2, kk);
       const int sl = __shfl_sync(0xffffffffu, slot, kk);
       const T* vr = v_cache + (size_t)sl * v_stride + (size_t)g * vdim;
@@ -292,6 +293,194 @@ diff_attn_kernel(T* __restrict__ out, int64_t ldo, const float* __restrict__ q, 
     }
 }
 
+// The same walk with the keys and values of a tile brought into shared memory first: TK = 32 S keys per tile, copied
+// asynchronously (16 bytes a piece, whole rows side by side) into one of two buffers while the other is consumed, so
+// that the cache is read once per CTA in full lines and lane = key reads its row from shared memory (rows padded by 16
+// bytes: no bank conflicts).  Needs K and V head rows that are multiples of 16 bytes.
+__device__ __forceinline__ void cp_async16_plain(void* smem_dst, const void* gsrc) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(smem_dst)), "l"(gsrc) : "memory");
+}
+
+template <typename T, int NCH>
+__global__ void __launch_bounds__(256)
+diff_attn_staged_kernel(T* __restrict__ out, int64_t ldo, const float* __restrict__ q, const T* __restrict__ k_cache,
+                        const T* __restrict__ v_cache, const T* __restrict__ gate, int64_t ldg,
+                        const int* __restrict__ q_cu, const int* __restrict__ kv_cu,
+                        const int* __restrict__ block_tables, const int* __restrict__ cu_block_lens,
+                        const int* __restrict__ token_seq, int H, int G, int dim, int vdim, int block_size,
+                        float scale, int window, int keep_first, float lambda, float out_scale, float eps, int RH,
+                        int S) {
+  extern __shared__ __align__(16) float sm[];
+  constexpr int EPC = 16 / (int)sizeof(T);           // elements per 16-byte piece
+  const int n_warps = RH * S, TK = 32 * S;
+  const int KROW = 2 * dim + EPC, VROW = vdim + EPC; // elements per staged row
+  float* q_s = sm;                                   // [RH][2 * dim]
+  float* acc_s = q_s + RH * 2 * dim;                 // [n_warps][2][vdim]
+  float* ml_s = acc_s + n_warps * 2 * vdim;          // [n_warps][4]
+  T* Kst = reinterpret_cast<T*>(ml_s + ((n_warps * 4 + 3) / 4) * 4);   // [2][TK][KROW]
+  T* Vst = Kst + (size_t)2 * TK * KROW;                                // [2][TK][VROW]
+  const int row = blockIdx.x, g = blockIdx.y, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int R = H / G;
+  const int r = warp % RH, sp = warp / RH;
+  const int h_local = blockIdx.z * RH + r;
+  const bool head_ok = h_local < R;
+  const int h = g * R + (head_ok ? h_local : 0);
+  const int seq = token_seq[row];
+  const int kv_len = kv_cu[seq + 1] - kv_cu[seq], q_len = q_cu[seq + 1] - q_cu[seq];
+  const int i = kv_len - q_len + (row - q_cu[seq]);
+  const int* table = block_tables + cu_block_lens[seq];
+  for (int d = threadIdx.x; d < RH * 2 * dim; d += blockDim.x) {
+    const int rr = d / (2 * dim), hh = blockIdx.z * RH + rr;
+    q_s[d] = hh < R ? q[((size_t)row * H + g * R + hh) * 2 * dim + (d - rr * 2 * dim)] : 0.0f;
+  }
+  const int lo = (window > 0 && i - window + 1 > 0) ? i - window + 1 : 0;
+  const int ns = keep_first < lo ? keep_first : lo;
+  const int total = ns + (i - lo + 1);
+  const int n_tiles = (total + TK - 1) / TK;
+  const size_t k_stride = (size_t)G * 2 * dim, v_stride = (size_t)G * vdim;
+  const int kp = 2 * dim / EPC, vp = vdim / EPC;     // 16-byte pieces per key row and value row
+  auto load_tile = [&](int idx, int buf) {
+    for (int key = warp; key < TK; key += n_warps) {
+      const int n = idx * TK + key;
+      // keys past the last one stand in as the row's own position (always written) and get weight 0
+      const int j = n < total ? (n < ns ? n : lo + (n - ns)) : i;
+      const size_t slot = (size_t)table[j / block_size] + j % block_size;
+      const T* kr = k_cache + slot * k_stride + (size_t)g * 2 * dim;
+      const T* vr = v_cache + slot * v_stride + (size_t)g * vdim;
+      T* kd = Kst + ((size_t)buf * TK + key) * KROW;
+      T* vd = Vst + ((size_t)buf * TK + key) * VROW;
+      for (int c = lane; c < kp + vp; c += 32) {
+        if (c < kp) cp_async16_plain(kd + c * EPC, kr + c * EPC);
+        else cp_async16_plain(vd + (c - kp) * EPC, vr + (c - kp) * EPC);
+      }
+    }
+  };
+  load_tile(0, 0);
+  asm volatile("cp.async.commit_group;" ::: "memory");
+  const float* q1 = q_s + r * 2 * dim;
+  const float* q2 = q1 + dim;
+  float m1 = -INFINITY, l1 = 0.0f, m2 = -INFINITY, l2 = 0.0f;
+  float a1[4 * NCH], a2[4 * NCH];
+#pragma unroll
+  for (int c = 0; c < 4 * NCH; ++c) a1[c] = a2[c] = 0.0f;
+  for (int it = 0; it < n_tiles; ++it) {
+    const int buf = it & 1;
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    __syncthreads();
+    if (it + 1 < n_tiles) load_tile(it + 1, buf ^ 1);
+    asm volatile("cp.async.commit_group;" ::: "memory");
+    const int n0 = it * TK + sp * 32;
+    if (n0 >= total) continue;                         // this split has no key in the last tile
+    const bool live = n0 + lane < total;
+    const T* kr = Kst + ((size_t)buf * TK + sp * 32 + lane) * KROW;
+    float s1 = -INFINITY, s2 = -INFINITY;
+    if (live) {
+      float d1 = 0.0f, d2 = 0.0f;
+      for (int d = 0; d < dim; d += 4) {
+        float x[4], y[4];
+        load4<T>(kr + d, x);
+        load4<T>(kr + dim + d, y);
+        const float4 u = *reinterpret_cast<const float4*>(q1 + d), w = *reinterpret_cast<const float4*>(q2 + d);
+        d1 += u.x * x[0]; d1 += u.y * x[1]; d1 += u.z * x[2]; d1 += u.w * x[3];
+        d2 += w.x * y[0]; d2 += w.y * y[1]; d2 += w.z * y[2]; d2 += w.w * y[3];
+      }
+      s1 = d1 * scale;
+      s2 = d2 * scale;
+    }
+    float t1 = s1, t2 = s2;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      t1 = fmaxf(t1, __shfl_xor_sync(0xffffffffu, t1, o));
+      t2 = fmaxf(t2, __shfl_xor_sync(0xffffffffu, t2, o));
+    }
+    const float nm1 = fmaxf(m1, t1), nm2 = fmaxf(m2, t2);
+    const float c1 = expf(m1 - nm1), c2 = expf(m2 - nm2);
+    const float p1 = live ? expf(s1 - nm1) : 0.0f, p2 = live ? expf(s2 - nm2) : 0.0f;
+    l1 = l1 * c1 + warp_sum(p1);
+    l2 = l2 * c2 + warp_sum(p2);
+    m1 = nm1;
+    m2 = nm2;
+#pragma unroll
+    for (int c = 0; c < 4 * NCH; ++c) { a1[c] *= c1; a2[c] *= c2; }
+    const T* vbase = Vst + ((size_t)buf * TK + sp * 32) * VROW;
+#pragma unroll 8
+    for (int kk = 0; kk < 32; ++kk) {
+      const float w1 = __shfl_sync(0xffffffffu, p1, kk), w2 = __shfl_sync(0xffffffffu, p2, kk);
+      const T* vr = vbase + (size_t)kk * VROW;
+#pragma unroll
+      for (int c = 0; c < NCH; ++c) {
+        const int col = (c * 32 + lane) * 4;
+        if (col < vdim) {
+          float v[4];
+          load4<T>(vr + col, v);
+#pragma unroll
+          for (int e = 0; e < 4; ++e) { a1[c * 4 + e] += w1 * v[e]; a2[c * 4 + e] += w2 * v[e]; }
+        }
+      }
+    }
+  }
+  asm volatile("cp.async.wait_group 0;" ::: "memory");
+  if (lane == 0) {
+    ml_s[warp * 4 + 0] = m1; ml_s[warp * 4 + 1] = l1; ml_s[warp * 4 + 2] = m2; ml_s[warp * 4 + 3] = l2;
+  }
+#pragma unroll
+  for (int c = 0; c < NCH; ++c)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const int col = (c * 32 + lane) * 4 + e;
+      if (col < vdim) {
+        acc_s[(warp * 2 + 0) * vdim + col] = a1[c * 4 + e];
+        acc_s[(warp * 2 + 1) * vdim + col] = a2[c * 4 + e];
+      }
+    }
+  __syncthreads();
+  if (sp != 0 || !head_ok) return;
+  float M1 = -INFINITY, M2 = -INFINITY;
+  for (int k = 0; k < S; ++k) {
+    M1 = fmaxf(M1, ml_s[(r + k * RH) * 4]);
+    M2 = fmaxf(M2, ml_s[(r + k * RH) * 4 + 2]);
+  }
+  float L1 = 0.0f, L2 = 0.0f, o[4 * NCH], x2[4 * NCH];
+#pragma unroll
+  for (int c = 0; c < 4 * NCH; ++c) o[c] = x2[c] = 0.0f;
+  for (int k = 0; k < S; ++k) {
+    const int w = r + k * RH;
+    const float f1 = ml_s[w * 4 + 1] > 0.0f ? expf(ml_s[w * 4] - M1) : 0.0f;
+    const float f2 = ml_s[w * 4 + 3] > 0.0f ? expf(ml_s[w * 4 + 2] - M2) : 0.0f;
+    L1 += f1 * ml_s[w * 4 + 1];
+    L2 += f2 * ml_s[w * 4 + 3];
+#pragma unroll
+    for (int c = 0; c < NCH; ++c)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int col = (c * 32 + lane) * 4 + e;
+        if (col < vdim) {
+          o[c * 4 + e] += f1 * acc_s[(w * 2 + 0) * vdim + col];
+          x2[c * 4 + e] += f2 * acc_s[(w * 2 + 1) * vdim + col];
+        }
+      }
+  }
+  float ss = 0.0f;
+#pragma unroll
+  for (int c = 0; c < NCH; ++c)
+#pragma unroll
+    for (int e = 0; e < 4; ++e)
+      if ((c * 32 + lane) * 4 + e < vdim) {
+        o[c * 4 + e] = o[c * 4 + e] / L1 - lambda * (x2[c * 4 + e] / L2);
+        ss += o[c * 4 + e] * o[c * 4 + e];
+      }
+  ss = warp_sum(ss);
+  const float gl = gate ? 1.0f / (1.0f + expf(-Num<T>::to_f(gate[(size_t)row * ldg + h]))) : 1.0f;
+  const float f = out_scale * gl / sqrtf(ss / (float)vdim + eps);
+#pragma unroll
+  for (int c = 0; c < NCH; ++c)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const int col = (c * 32 + lane) * 4 + e;
+      if (col < vdim) out[(size_t)row * ldo + (size_t)h * vdim + col] = Num<T>::from_f(o[c * 4 + e] * f);
+    }
+}
+
 // ------------------------------------------------------------------------------------------------------------
 // Prompt portions in bf16 on the tensor cores (mma.sync m16n8k16, fp32 accumulation).
 // One CTA = 4 warps = RW query heads of one key/value group x (4 / RW) sub-tiles of 16 consecutive tokens of one
@@ -319,7 +508,7 @@ __device__ __forceinline__ void ldsm_x4_t(uint32_t (&r)[4], const void* p) {
                : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_u32(p)));
 }
 __device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
-  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+  asm("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
                : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
                : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
@@ -398,6 +587,8 @@ diff_attn_prefill_kernel(__nv_bfloat16* __restrict__ out, int64_t ldo, const flo
   int pos[2];
 #pragma unroll
   for (int r2 = 0; r2 < 2; ++r2) pos[r2] = (row_t[r2] < q_len && head_ok) ? first_pos + row_t[r2] : -1;
+  const int wpos0 = first_pos + t0 + ts * 16;          // position of the warp's first row
+  const bool warp_rows_valid = head_ok && t0 + ts * 16 + 15 < q_len;
   float mx[2][2], ls[2][2];                            // [map][row]
   float o[2][VT_MAX * 2][4];
 #pragma unroll
@@ -415,6 +606,10 @@ diff_attn_prefill_kernel(__nv_bfloat16* __restrict__ out, int64_t ldo, const flo
     if (it + 1 < n_tiles) load_tile(it + 1, buf ^ 1);
     cp_async_commit();
     const int j0 = tile_j0(it);
+    // every key of the tile visible from every row of this warp: all 16 rows valid, the tile's last key not after
+    // the warp's first row, and its first key inside the window of the warp's last row (or the tile all kept)
+    const bool full_tile = warp_rows_valid && j0 + kBK - 1 <= wpos0 &&
+                           (window <= 0 || wpos0 + 15 - j0 < window || j0 + kBK - 1 < keep_first);
     const __nv_bfloat16* kt = Ks + (size_t)buf * kBK * KROW;
     const __nv_bfloat16* vt = Vs + (size_t)buf * kBK * VROW;
 #pragma unroll
@@ -436,18 +631,28 @@ diff_attn_prefill_kernel(__nv_bfloat16* __restrict__ out, int64_t ldo, const flo
           }
         }
       }
-      // visibility, running maximum and sum
+      // visibility (tested per element only on tiles that some row of the warp sees in part), running maximum
       float rmax[2] = {-INFINITY, -INFINITY};
+      if (full_tile) {
 #pragma unroll
-      for (int n = 0; n < 4; ++n)
+        for (int n = 0; n < 4; ++n)
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const int j = j0 + n * 8 + qc + (e & 1), i = pos[e >> 1];
-          const bool vis = j <= i && (window <= 0 || i - j < window || j < keep_first);
-          const float v = vis ? sc[n][e] * scale : -INFINITY;
-          sc[n][e] = v;
-          rmax[e >> 1] = fmaxf(rmax[e >> 1], v);
-        }
+          for (int e = 0; e < 4; ++e) {
+            sc[n][e] *= scale;
+            rmax[e >> 1] = fmaxf(rmax[e >> 1], sc[n][e]);
+          }
+      } else {
+#pragma unroll
+        for (int n = 0; n < 4; ++n)
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const int j = j0 + n * 8 + qc + (e & 1), i = pos[e >> 1];
+            const bool vis = j <= i && (window <= 0 || i - j < window || j < keep_first);
+            const float v = vis ? sc[n][e] * scale : -INFINITY;
+            sc[n][e] = v;
+            rmax[e >> 1] = fmaxf(rmax[e >> 1], v);
+          }
+      }
       float corr[2], msafe[2];
 #pragma unroll
       for (int r2 = 0; r2 < 2; ++r2) {
@@ -455,37 +660,52 @@ diff_attn_prefill_kernel(__nv_bfloat16* __restrict__ out, int64_t ldo, const flo
         rmax[r2] = fmaxf(rmax[r2], __shfl_xor_sync(0xffffffffu, rmax[r2], 2));
         const float nm = fmaxf(mx[m][r2], rmax[r2]);
         msafe[r2] = nm == -INFINITY ? 0.0f : nm;
-        corr[r2] = expf(mx[m][r2] - msafe[r2]);
+        corr[r2] = __expf(mx[m][r2] - msafe[r2]);
         mx[m][r2] = nm;
         ls[m][r2] *= corr[r2];
       }
+      if (__any_sync(0xffffffffu, corr[0] != 1.0f || corr[1] != 1.0f)) {   // the maximum settles after a few tiles
 #pragma unroll
-      for (int n = 0; n < VT_MAX * 2; ++n) {
-        o[m][n][0] *= corr[0]; o[m][n][1] *= corr[0];
-        o[m][n][2] *= corr[1]; o[m][n][3] *= corr[1];
+        for (int n = 0; n < VT_MAX * 2; ++n) {
+          o[m][n][0] *= corr[0]; o[m][n][1] *= corr[0];
+          o[m][n][2] *= corr[1]; o[m][n][3] *= corr[1];
+        }
       }
       uint32_t phi[2][4], plo[2][4];                   // A fragments of the two 16-key steps
 #pragma unroll
       for (int n = 0; n < 4; ++n) {
-        const float p0 = expf(sc[n][0] - msafe[0]), p1 = expf(sc[n][1] - msafe[0]);
-        const float p2 = expf(sc[n][2] - msafe[1]), p3 = expf(sc[n][3] - msafe[1]);
+        const float p0 = __expf(sc[n][0] - msafe[0]), p1 = __expf(sc[n][1] - msafe[0]);   // 2 ulp: the products are bf16
+        const float p2 = __expf(sc[n][2] - msafe[1]), p3 = __expf(sc[n][3] - msafe[1]);
         ls[m][0] += p0 + p1;
         ls[m][1] += p2 + p3;
         const int kk = n >> 1, half = (n & 1) * 2;
         split_bf16(p0, p1, phi[kk][half], plo[kk][half]);
         split_bf16(p2, p3, phi[kk][half + 1], plo[kk][half + 1]);
       }
+      // four independent accumulators between two products into the same one (hi terms of a 32-channel strip,
+      // then its lo terms)
 #pragma unroll
       for (int kk = 0; kk < 2; ++kk)
 #pragma unroll
-        for (int vt16 = 0; vt16 < VT_MAX; ++vt16) {
-          if (vt16 < VT) {
-            uint32_t b[4];
-            ldsm_x4_t(b, vt + (kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * VROW + vt16 * 16 + (lane >> 4) * 8);
-            mma_bf16(o[m][vt16 * 2], phi[kk], b[0], b[1]);
-            mma_bf16(o[m][vt16 * 2], plo[kk], b[0], b[1]);
-            mma_bf16(o[m][vt16 * 2 + 1], phi[kk], b[2], b[3]);
-            mma_bf16(o[m][vt16 * 2 + 1], plo[kk], b[2], b[3]);
+        for (int vp = 0; vp < VT_MAX; vp += 2) {
+          if (vp < VT) {
+            const bool two = vp + 1 < VT;
+            uint32_t b0[4], b1[4] = {0u, 0u, 0u, 0u};
+            const __nv_bfloat16* vrow = vt + (kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * VROW + (lane >> 4) * 8;
+            ldsm_x4_t(b0, vrow + vp * 16);
+            if (two) ldsm_x4_t(b1, vrow + (vp + 1) * 16);
+            mma_bf16(o[m][vp * 2], phi[kk], b0[0], b0[1]);
+            mma_bf16(o[m][vp * 2 + 1], phi[kk], b0[2], b0[3]);
+            if (two) {
+              mma_bf16(o[m][vp * 2 + 2], phi[kk], b1[0], b1[1]);
+              mma_bf16(o[m][vp * 2 + 3], phi[kk], b1[2], b1[3]);
+            }
+            mma_bf16(o[m][vp * 2], plo[kk], b0[0], b0[1]);
+            mma_bf16(o[m][vp * 2 + 1], plo[kk], b0[2], b0[3]);
+            if (two) {
+              mma_bf16(o[m][vp * 2 + 2], plo[kk], b1[0], b1[1]);
+              mma_bf16(o[m][vp * 2 + 3], plo[kk], b1[2], b1[3]);
+            }
           }
         }
     }
@@ -587,6 +807,40 @@ int b200_diff_attn(void* out, int64_t ldo, const float* q, const void* k_cache, 
                    is_aligned(k_cache, 16) && is_aligned(v_cache, 16);
   const int nch = vdim <= 128 ? 1 : (vdim <= 256 ? 2 : 4);
   dim3 grid((unsigned)rows, (unsigned)G, (unsigned)chunks);
+  // rows of whole 16-byte pieces: the keys and values of a tile go through shared memory
+  if (vec && (2 * dim * esz) % 16 == 0 && (vdim * esz) % 16 == 0) {
+    const int RHs = R < 8 ? R : 8, Ss = 8 / RHs, TK = 32 * Ss, ch = (R + RHs - 1) / RHs, epc = 16 / esz;
+    const size_t smem_s = (size_t)(RHs * 2 * dim + RHs * Ss * 2 * vdim + ((RHs * Ss * 4 + 3) / 4) * 4) * sizeof(float) +
+                          (size_t)2 * TK * (2 * dim + epc + vdim + epc) * esz;
+    if (smem_s <= 200 * 1024 && ch <= 65535) {
+      dim3 grid_s((unsigned)rows, (unsigned)G, (unsigned)ch);
+#define DAS_LAUNCH(T, NCH)                                                                                     \
+  do {                                                                                                         \
+    if (smem_s > 48 * 1024)                                                                                    \
+      B200_CUDA_OK(cudaFuncSetAttribute(diff_attn_staged_kernel<T, NCH>,                                       \
+                                        cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_s));            \
+    diff_attn_staged_kernel<T, NCH><<<grid_s, RHs * Ss * 32, smem_s, st>>>(                                    \
+        static_cast<T*>(out), ldo, q, static_cast<const T*>(k_cache), static_cast<const T*>(v_cache),         \
+        static_cast<const T*>(gate), ldg, q_cu_lens, kv_cu_lens, block_tables, cu_block_lens, token_seq,      \
+        (int)H, (int)G, (int)dim, (int)vdim, (int)block_size, scale, (int)window, (int)keep_first, lambda,    \
+        out_scale, eps, RHs, Ss);                                                                              \
+  } while (0)
+#define DAS_CALL(T)                                                                                            \
+  do {                                                                                                         \
+    if (nch == 1) DAS_LAUNCH(T, 1); else if (nch == 2) DAS_LAUNCH(T, 2); else DAS_LAUNCH(T, 4);                \
+  } while (0)
+      switch (dtype) {
+        case B200_BF16: DAS_CALL(__nv_bfloat16); break;
+        case B200_FP16: DAS_CALL(__half); break;
+        case B200_FP32: DAS_CALL(float); break;
+        default: return set_error(B200_ERR_INVALID_ARG, "bad dtype %d", dtype);
+      }
+#undef DAS_CALL
+#undef DAS_LAUNCH
+      B200_LAUNCH_OK("diff_attn_staged_kernel");
+      return B200_OK;
+    }
+  }
 #define DA_LAUNCH(T, NCH, VEC)                                                                                 \
   do {                                                                                                         \
     if (smem > 48 * 1024)                                                                                      \

@@ -953,17 +953,34 @@ def token_gated_gelu(a: torch.Tensor, table: torch.Tensor, col0: int, tokens: to
 # ---------------------------------------------------------------------------
 # minimal gated recurrent unit (csrc/mingru.cu)
 # ---------------------------------------------------------------------------
+# portions at least this long are cut into chunks of MINGRU_CHUNK tokens that run side by side
+MINGRU_CHUNKED_MIN_ROWS = 128
+MINGRU_CHUNK = 64
+
+
 def mingru_scan(proj: torch.Tensor, z_bias: Optional[torch.Tensor], x_bias: Optional[torch.Tensor],
                 state: torch.Tensor, q_cu: torch.Tensor, positions: torch.Tensor, state_slots: torch.Tensor,
-                n_seq: int, width: int) -> torch.Tensor:
-    """proj [rows, >= 3 width] = [z | x | g]; returns S_t * silu(g_t) [rows, width]; state fp32 [slots, width]."""
+                n_seq: int, width: int, q_max: int = 0, chunk_len: int = 0) -> torch.Tensor:
+    """proj [rows, >= 3 width] = [z | x | g]; returns S_t * silu(g_t) [rows, width]; state fp32 [slots, width].
+    q_max (host number: the step's longest portion): long portions run as chunks side by side (chunk_len, default
+    MINGRU_CHUNK, forces it)."""
     _cuda(proj, state)
     _f32(z_bias, x_bias, state)
     _check_i32(q_cu, positions, state_slots)
     assert proj.dim() == 2 and proj.stride(1) == 1 and proj.shape[1] >= 3 * width and state.shape[1] == width
     out = torch.empty((proj.shape[0], width), dtype=proj.dtype, device=proj.device)
-    check(_lib.load().b200_mingru_scan(_p(out), width, _p(proj), proj.stride(0), _p(z_bias), _p(x_bias), _p(state),
-                                       _p(q_cu), _p(positions), _p(state_slots), n_seq, width, _dt(proj), _stream()))
+    lib = _lib.load()
+    if chunk_len > 0 or q_max >= MINGRU_CHUNKED_MIN_ROWS:
+        L = chunk_len or MINGRU_CHUNK
+        q_max = q_max or proj.shape[0]
+        n = lib.b200_mingru_chunked_workspace_floats(n_seq, width, q_max, L)
+        ws = torch.empty(n, dtype=torch.float32, device=proj.device)
+        check(lib.b200_mingru_scan_chunked(_p(out), width, _p(proj), proj.stride(0), _p(z_bias), _p(x_bias),
+                                           _p(state), _p(q_cu), _p(positions), _p(state_slots), n_seq, width, q_max,
+                                           L, _p(ws), n, _dt(proj), _stream()))
+        return out
+    check(lib.b200_mingru_scan(_p(out), width, _p(proj), proj.stride(0), _p(z_bias), _p(x_bias), _p(state),
+                               _p(q_cu), _p(positions), _p(state_slots), n_seq, width, _dt(proj), _stream()))
     return out
 
 

@@ -815,7 +815,8 @@ class MinGRUMixer:
 
     def forward(self, h: torch.Tensor, positions: torch.Tensor, params: InputParameters) -> torch.Tensor:
         o = kernels.mingru_scan(self.in_proj(h), self.z_bias, self.x_bias, self.state, params.q_cu_seq_lens,
-                                positions, params.state_slots, params.num_sequences, self.width)
+                                positions, params.state_slots, params.num_sequences, self.width,
+                                params.q_max_seq_len)
         return self.o_proj(o)
 
     __call__ = forward

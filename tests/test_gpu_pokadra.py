@@ -151,7 +151,9 @@ def test_mingru_in_portions_from_a_dirty_slot(dtype, width):
     for k, size in enumerate((33, 2, 1, 1, 30)):
         (_, pos, par), _ = _params([size, 3], [at, 0], slots=[2, 0])
         rows = torch.cat([proj[at:at + size], proj[:3]]).to(DEV)
-        o = kernels.mingru_scan(rows, bz.to(DEV), bx.to(DEV), state, par.q_cu_seq_lens, pos, par.state_slots, 2, width)
+        # the last portion runs as chunks of 7 tokens side by side (3 of the second sequence's tokens fill less than one)
+        o = kernels.mingru_scan(rows, bz.to(DEV), bx.to(DEV), state, par.q_cu_seq_lens, pos, par.state_slots, 2, width,
+                                q_max=size, chunk_len=7 if k == 4 else 0)
         got.append(o[:size].float().cpu())
         assert float((o[size:].cpu().double() - ref[:3]).abs().max()) < tol
         at += size
@@ -270,6 +272,20 @@ def test_prefill_decode_and_portions_agree_with_the_oracle(name, dtype):
     want = oracle_logits(oracle, tokens)
     for cuts in ([90], [58], [1] * 3, [2, 2, 5, 2, 31, 1, 2, 17, 2], [7] * 13, [33, 4, 4, 4, 40]):
         eng = engine_for(model, block_size=4)
+        got = run_schedule(eng, tokens, cuts)
+        assert pc.logits_error(got, want) < TOL[dtype], cuts
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_long_portions_run_in_chunks(dtype):
+    """Portions long enough for the chunked recurrence and for many key tiles, cut at places that are no multiple of
+    the chunk or the tile, against the whole prompt in one step and the oracle."""
+    cfg = pc.CONFIGS["mix"]
+    model, oracle = build(cfg, dtype, seed=6)
+    tokens = toks(333, cfg["vocab"], 7)
+    want = oracle_logits(oracle, tokens)
+    for cuts in ([333], [150, 2, 181], [129, 130, 71]):
+        eng = engine_for(model, max_tokens=400, block_size=16)
         got = run_schedule(eng, tokens, cuts)
         assert pc.logits_error(got, want) < TOL[dtype], cuts
 
