@@ -746,6 +746,225 @@ diff_attn_prefill_kernel(__nv_bfloat16* __restrict__ out, int64_t ldo, const flo
   }
 }
 
+// ------------------------------------------------------------------------------------------------------------
+// Single tokens in bf16 on the tensor cores: the 16 rows of the product are the query HEADS of one key/value group
+// (all at the row's position), so one pass over the group's keys serves every head that shares them.  One CTA per
+// (row, group[, chunk of 16 heads]); tiles of 64 keys are staged as above and each of the 4 warps takes 16 keys of
+// every tile with accumulators of its own; the warps' running maxima, sums and weighted sums are merged through
+// shared memory at the end.
+// ------------------------------------------------------------------------------------------------------------
+constexpr int kDK = 64;
+
+template <int KS_MAX, int VT_MAX>
+__global__ void __launch_bounds__(128)
+diff_attn_decode_tc_kernel(__nv_bfloat16* __restrict__ out, int64_t ldo, const float* __restrict__ q,
+                           const __nv_bfloat16* __restrict__ k_cache, const __nv_bfloat16* __restrict__ v_cache,
+                           const __nv_bfloat16* __restrict__ gate, int64_t ldg, const int* __restrict__ q_cu,
+                           const int* __restrict__ kv_cu, const int* __restrict__ block_tables,
+                           const int* __restrict__ cu_block_lens, const int* __restrict__ token_seq, int H, int G,
+                           int dim, int vdim, int block_size, float scale, int window, int keep_first, float lambda,
+                           float out_scale, float eps, int tile_bytes) {
+  extern __shared__ __align__(16) unsigned char smraw[];
+  const int KROW = 2 * dim + 8, VROW = vdim + 8;
+  __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(smraw);     // [16][KROW]
+  float* ml_s = reinterpret_cast<float*>(Qs + 16 * KROW);          // [4 warps][2 maps][2: m, l][16 rows]
+  unsigned char* big = reinterpret_cast<unsigned char*>(ml_s + 4 * 2 * 2 * 16);
+  __nv_bfloat16* Ks = reinterpret_cast<__nv_bfloat16*>(big);       // [2][kDK][KROW]
+  __nv_bfloat16* Vs = Ks + 2 * kDK * KROW;                         // [2][kDK][VROW]
+  float* o_s = reinterpret_cast<float*>(big);                      // after the walk: [4 warps][2 maps][16][vdim]
+  (void)tile_bytes;
+  const int row = blockIdx.x, g = blockIdx.y, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int R = H / G, h_base = blockIdx.z * 16;
+  const int n_heads = R - h_base < 16 ? R - h_base : 16;           // valid rows of the tile
+  const int seq = token_seq[row];
+  const int kv_len = kv_cu[seq + 1] - kv_cu[seq], q_len = q_cu[seq + 1] - q_cu[seq];
+  const int i = kv_len - q_len + (row - q_cu[seq]);
+  const int KS = dim / 16, VT = vdim / 16;
+  const int* table = block_tables + cu_block_lens[seq];
+  for (int e = threadIdx.x; e < 16 * 2 * dim; e += 128) {
+    const int rr = e / (2 * dim), d = e - rr * 2 * dim;
+    const float v = rr < n_heads ? q[((size_t)row * H + g * R + h_base + rr) * 2 * dim + d] : 0.0f;
+    Qs[rr * KROW + d] = __float2bfloat16_rn(v);
+  }
+  const int lo = (window > 0 && i - window + 1 > 0) ? i - window + 1 : 0;
+  const int ns = keep_first < lo ? keep_first : lo;
+  const int sink_tiles = (ns + kDK - 1) / kDK;
+  const int wt0 = lo / kDK > sink_tiles ? lo / kDK : sink_tiles;
+  const int n_tiles = sink_tiles + (i / kDK - wt0 + 1);
+  auto tile_j0 = [&](int idx) { return (idx < sink_tiles ? idx : wt0 + idx - sink_tiles) * kDK; };
+  const size_t k_stride = (size_t)G * 2 * dim, v_stride = (size_t)G * vdim;
+  auto load_tile = [&](int idx, int buf) {
+    const int j0 = tile_j0(idx);
+    const int sub = threadIdx.x & 1;
+    for (int key = threadIdx.x >> 1; key < kDK; key += 64) {
+      const int j = j0 + key;
+      const bool ok = j <= i;
+      size_t slot = 0;
+      if (ok) slot = (size_t)table[j / block_size] + j % block_size;
+      const __nv_bfloat16* kr = k_cache + slot * k_stride + (size_t)g * 2 * dim;
+      const __nv_bfloat16* vr = v_cache + slot * v_stride + (size_t)g * vdim;
+      __nv_bfloat16* kd = Ks + ((size_t)buf * kDK + key) * KROW;
+      __nv_bfloat16* vd = Vs + ((size_t)buf * kDK + key) * VROW;
+      for (int c = sub; c < dim / 4; c += 2) cp_async16(kd + c * 8, kr + c * 8, ok);
+      for (int c = sub; c < vdim / 8; c += 2) cp_async16(vd + c * 8, vr + c * 8, ok);
+    }
+  };
+  load_tile(0, 0);
+  cp_async_commit();
+  const int gr = lane >> 2, qc = (lane & 3) * 2;
+  float mx[2][2], ls[2][2];
+  float o[2][VT_MAX * 2][4];
+#pragma unroll
+  for (int m = 0; m < 2; ++m) {
+    mx[m][0] = mx[m][1] = -INFINITY;
+    ls[m][0] = ls[m][1] = 0.0f;
+#pragma unroll
+    for (int n = 0; n < VT_MAX * 2; ++n) o[m][n][0] = o[m][n][1] = o[m][n][2] = o[m][n][3] = 0.0f;
+  }
+  for (int it = 0; it < n_tiles; ++it) {
+    const int buf = it & 1;
+    cp_async_wait_all();
+    __syncthreads();
+    if (it + 1 < n_tiles) load_tile(it + 1, buf ^ 1);
+    cp_async_commit();
+    const int j0 = tile_j0(it) + warp * 16;              // this warp's 16 keys of the tile
+    if (j0 > i) continue;                                // all after the row's position
+    const __nv_bfloat16* kt = Ks + ((size_t)buf * kDK + warp * 16) * KROW;
+    const __nv_bfloat16* vt = Vs + ((size_t)buf * kDK + warp * 16) * VROW;
+#pragma unroll
+    for (int m = 0; m < 2; ++m) {
+      float sc[2][4];
+#pragma unroll
+      for (int n = 0; n < 2; ++n) sc[n][0] = sc[n][1] = sc[n][2] = sc[n][3] = 0.0f;
+#pragma unroll
+      for (int ks = 0; ks < KS_MAX; ++ks) {
+        if (ks < KS) {
+          uint32_t a[4], b[4];
+          ldsm_x4(a, Qs + (lane & 15) * KROW + m * dim + ks * 16 + (lane >> 4) * 8);
+          ldsm_x4(b, kt + ((lane & 7) + (lane >> 4) * 8) * KROW + m * dim + ks * 16 + ((lane >> 3) & 1) * 8);
+          mma_bf16(sc[0], a, b[0], b[1]);
+          mma_bf16(sc[1], a, b[2], b[3]);
+        }
+      }
+      float rmax[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+      for (int n = 0; n < 2; ++n)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int j = j0 + n * 8 + qc + (e & 1);
+          const bool vis = j <= i && (window <= 0 || i - j < window || j < keep_first);
+          const float v = vis ? sc[n][e] * scale : -INFINITY;
+          sc[n][e] = v;
+          rmax[e >> 1] = fmaxf(rmax[e >> 1], v);
+        }
+      float corr[2], msafe[2];
+#pragma unroll
+      for (int r2 = 0; r2 < 2; ++r2) {
+        rmax[r2] = fmaxf(rmax[r2], __shfl_xor_sync(0xffffffffu, rmax[r2], 1));
+        rmax[r2] = fmaxf(rmax[r2], __shfl_xor_sync(0xffffffffu, rmax[r2], 2));
+        const float nm = fmaxf(mx[m][r2], rmax[r2]);
+        msafe[r2] = nm == -INFINITY ? 0.0f : nm;
+        corr[r2] = __expf(mx[m][r2] - msafe[r2]);
+        mx[m][r2] = nm;
+        ls[m][r2] *= corr[r2];
+      }
+      if (__any_sync(0xffffffffu, corr[0] != 1.0f || corr[1] != 1.0f)) {
+#pragma unroll
+        for (int n = 0; n < VT_MAX * 2; ++n) {
+          o[m][n][0] *= corr[0]; o[m][n][1] *= corr[0];
+          o[m][n][2] *= corr[1]; o[m][n][3] *= corr[1];
+        }
+      }
+      uint32_t phi[4], plo[4];
+#pragma unroll
+      for (int n = 0; n < 2; ++n) {
+        const float p0 = __expf(sc[n][0] - msafe[0]), p1 = __expf(sc[n][1] - msafe[0]);
+        const float p2 = __expf(sc[n][2] - msafe[1]), p3 = __expf(sc[n][3] - msafe[1]);
+        ls[m][0] += p0 + p1;
+        ls[m][1] += p2 + p3;
+        split_bf16(p0, p1, phi[n * 2], plo[n * 2]);
+        split_bf16(p2, p3, phi[n * 2 + 1], plo[n * 2 + 1]);
+      }
+#pragma unroll
+      for (int vt16 = 0; vt16 < VT_MAX; ++vt16) {
+        if (vt16 < VT) {
+          uint32_t b[4];
+          ldsm_x4_t(b, vt + ((lane & 7) + ((lane >> 3) & 1) * 8) * VROW + vt16 * 16 + (lane >> 4) * 8);
+          mma_bf16(o[m][vt16 * 2], phi, b[0], b[1]);
+          mma_bf16(o[m][vt16 * 2 + 1], phi, b[2], b[3]);
+          mma_bf16(o[m][vt16 * 2], plo, b[0], b[1]);
+          mma_bf16(o[m][vt16 * 2 + 1], plo, b[2], b[3]);
+        }
+      }
+    }
+  }
+  cp_async_wait_all();
+  __syncthreads();                                       // the tiles are done with: their memory takes the partial sums
+#pragma unroll
+  for (int m = 0; m < 2; ++m)
+#pragma unroll
+    for (int r2 = 0; r2 < 2; ++r2) {
+      ls[m][r2] += __shfl_xor_sync(0xffffffffu, ls[m][r2], 1);
+      ls[m][r2] += __shfl_xor_sync(0xffffffffu, ls[m][r2], 2);
+      if ((lane & 3) == 0) {
+        ml_s[((warp * 2 + m) * 2 + 0) * 16 + gr + r2 * 8] = mx[m][r2];
+        ml_s[((warp * 2 + m) * 2 + 1) * 16 + gr + r2 * 8] = ls[m][r2];
+      }
+    }
+#pragma unroll
+  for (int m = 0; m < 2; ++m)
+#pragma unroll
+    for (int n = 0; n < VT_MAX * 2; ++n)
+      if (n < VT * 2) {
+        float* dst = o_s + ((size_t)(warp * 2 + m) * 16) * vdim + n * 8 + qc;
+        dst[(size_t)gr * vdim] = o[m][n][0];
+        dst[(size_t)gr * vdim + 1] = o[m][n][1];
+        dst[(size_t)(gr + 8) * vdim] = o[m][n][2];
+        dst[(size_t)(gr + 8) * vdim + 1] = o[m][n][3];
+      }
+  __syncthreads();
+  // warp w finishes heads w, w + 4, ...: lanes over the value channels
+  for (int rr = warp; rr < n_heads; rr += 4) {
+    float M[2] = {-INFINITY, -INFINITY}, L[2] = {0.0f, 0.0f}, f[2][4];
+#pragma unroll
+    for (int m = 0; m < 2; ++m) {
+#pragma unroll
+      for (int w = 0; w < 4; ++w) M[m] = fmaxf(M[m], ml_s[((w * 2 + m) * 2 + 0) * 16 + rr]);
+#pragma unroll
+      for (int w = 0; w < 4; ++w) {
+        const float lw = ml_s[((w * 2 + m) * 2 + 1) * 16 + rr];
+        f[m][w] = lw > 0.0f ? expf(ml_s[((w * 2 + m) * 2 + 0) * 16 + rr] - M[m]) : 0.0f;
+        L[m] += f[m][w] * lw;
+      }
+    }
+    float d[4], ss = 0.0f;                               // vdim <= 128: up to 4 channels per lane
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      const int col = lane + 32 * c;
+      d[c] = 0.0f;
+      if (col < vdim) {
+        float x1 = 0.0f, x2 = 0.0f;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+          x1 += f[0][w] * o_s[((size_t)(w * 2 + 0) * 16 + rr) * vdim + col];
+          x2 += f[1][w] * o_s[((size_t)(w * 2 + 1) * 16 + rr) * vdim + col];
+        }
+        d[c] = x1 / L[0] - lambda * (x2 / L[1]);
+        ss += d[c] * d[c];
+      }
+    }
+    ss = warp_sum(ss);
+    const int h = g * R + h_base + rr;
+    const float gl = gate ? 1.0f / (1.0f + expf(-__bfloat162float(gate[(size_t)row * ldg + h]))) : 1.0f;
+    const float fo = out_scale * gl / sqrtf(ss / (float)vdim + eps);
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      const int col = lane + 32 * c;
+      if (col < vdim) out[(size_t)row * ldo + (size_t)h * vdim + col] = __float2bfloat16_rn(d[c] * fo);
+    }
+  }
+}
+
 }  // namespace
 }  // namespace b200
 
@@ -921,6 +1140,52 @@ int b200_diff_attn_prefill(void* out, int64_t ldo, const float* q, const void* k
   else DAP_LAUNCH(8, 8);
 #undef DAP_LAUNCH
   B200_LAUNCH_OK("diff_attn_prefill_kernel");
+  return B200_OK;
+}
+
+}  // extern "C"
+
+extern "C" {
+
+int b200_diff_attn_decode_tc(void* out, int64_t ldo, const float* q, const void* k_cache, const void* v_cache,
+                             const void* gate, int64_t ldg, const int32_t* q_cu_lens, const int32_t* kv_cu_lens,
+                             const int32_t* block_tables, const int32_t* cu_block_lens, const int32_t* token_seq,
+                             int64_t rows, int64_t H, int64_t G, int64_t dim, int64_t vdim, int64_t block_size,
+                             float scale, int64_t window, int64_t keep_first, float lambda, float out_scale, float eps,
+                             int dtype, b200_stream_t stream) {
+  if (rows == 0) return B200_OK;
+  B200_CHECK_ARG(out && q && k_cache && v_cache && q_cu_lens && kv_cu_lens && block_tables && cu_block_lens &&
+                     token_seq, "diff_attn_decode_tc: null pointer");
+  if (!b200_diff_attn_prefill_supported(dim, vdim, dtype))
+    return set_error(B200_ERR_UNSUPPORTED, "diff_attn_decode_tc: bf16 with dim and vdim multiples of 16 up to 128");
+  B200_CHECK_ARG(rows > 0 && H > 0 && G > 0 && G <= 65535 && H % G == 0 && block_size > 0 && ldo >= H * vdim &&
+                     window >= 0 && window < (1ll << 31) && keep_first >= 0 && keep_first < (1ll << 31) &&
+                     is_aligned(k_cache, 16) && is_aligned(v_cache, 16),
+                 "diff_attn_decode_tc: bad shape or alignment");
+  auto st = static_cast<cudaStream_t>(stream);
+  const int R = (int)(H / G), chunks = (R + 15) / 16;
+  const size_t tiles = ((size_t)2 * kDK * (2 * dim + 8) + (size_t)2 * kDK * (vdim + 8)) * 2;
+  const size_t merge = (size_t)4 * 2 * 16 * vdim * sizeof(float);
+  const size_t big = tiles > merge ? tiles : merge;
+  const size_t smem = (size_t)16 * (2 * dim + 8) * 2 + 4 * 2 * 2 * 16 * sizeof(float) + big;
+  dim3 grid((unsigned)rows, (unsigned)G, (unsigned)chunks);
+#define DAD_LAUNCH(KS, VT)                                                                                     \
+  do {                                                                                                         \
+    if (smem > 48 * 1024)                                                                                      \
+      B200_CUDA_OK(cudaFuncSetAttribute(diff_attn_decode_tc_kernel<KS, VT>,                                    \
+                                        cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));              \
+    diff_attn_decode_tc_kernel<KS, VT><<<grid, 128, smem, st>>>(                                               \
+        static_cast<__nv_bfloat16*>(out), ldo, q, static_cast<const __nv_bfloat16*>(k_cache),                  \
+        static_cast<const __nv_bfloat16*>(v_cache), static_cast<const __nv_bfloat16*>(gate), ldg, q_cu_lens,   \
+        kv_cu_lens, block_tables, cu_block_lens, token_seq, (int)H, (int)G, (int)dim, (int)vdim,               \
+        (int)block_size, scale, (int)window, (int)keep_first, lambda, out_scale, eps, (int)tiles);             \
+  } while (0)
+  if (dim <= 64 && vdim <= 64) DAD_LAUNCH(4, 4);
+  else if (dim <= 64) DAD_LAUNCH(4, 8);
+  else if (vdim <= 64) DAD_LAUNCH(8, 4);
+  else DAD_LAUNCH(8, 8);
+#undef DAD_LAUNCH
+  B200_LAUNCH_OK("diff_attn_decode_tc_kernel");
   return B200_OK;
 }
 

@@ -1012,6 +1012,8 @@ def diff_attn_prepare(q_in: torch.Tensor, k_in: Optional[torch.Tensor], v_in: Op
 
 # a step whose longest portion has at least this many tokens runs the tensor-core kernel (bf16, fitting head sizes)
 DIFF_ATTN_PREFILL_MIN_ROWS = 4
+# single tokens in bf16 with at least this many query heads per key/value head run as tensor-core tiles of heads
+DIFF_ATTN_DECODE_TC_MIN_GROUP = 2
 
 
 def diff_attn(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, gate: Optional[torch.Tensor],
@@ -1030,13 +1032,21 @@ def diff_attn(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, gat
     assert gate is None or (gate.shape == (rows, H) and gate.stride(1) == 1 and gate.dtype == k_cache.dtype)
     out = torch.empty((rows, H * vdim), dtype=k_cache.dtype, device=q.device)
     lib = _lib.load()
-    if (n_seq > 0 and q_max >= DIFF_ATTN_PREFILL_MIN_ROWS and os.environ.get("B200_DIFF_ATTN_IMPL") != "simt"
+    impl = os.environ.get("B200_DIFF_ATTN_IMPL")      # "simt": CUDA cores throughout; "simt_decode": for single tokens
+    if (n_seq > 0 and q_max >= DIFF_ATTN_PREFILL_MIN_ROWS and impl != "simt"
             and lib.b200_diff_attn_prefill_supported(dim, vdim, _dt(k_cache))):
         check(lib.b200_diff_attn_prefill(_p(out), H * vdim, _p(q), _p(k_cache), _p(v_cache), _p(gate),
                                          gate.stride(0) if gate is not None else 0, _p(q_cu), _p(kv_cu),
                                          _p(block_tables), _p(cu_block_lens), n_seq, q_max, H, G, dim, vdim,
                                          block_size, scale, window, keep_first, lam, out_scale, eps, _dt(k_cache),
                                          _stream()))
+        return out
+    args = (_p(out), H * vdim, _p(q), _p(k_cache), _p(v_cache), _p(gate), gate.stride(0) if gate is not None else 0,
+            _p(q_cu), _p(kv_cu), _p(block_tables), _p(cu_block_lens), _p(token_seq), rows, H, G, dim, vdim, block_size,
+            scale, window, keep_first, lam, out_scale, eps, _dt(k_cache), _stream())
+    if (impl not in ("simt", "simt_decode") and H // G >= DIFF_ATTN_DECODE_TC_MIN_GROUP
+            and lib.b200_diff_attn_prefill_supported(dim, vdim, _dt(k_cache))):
+        check(lib.b200_diff_attn_decode_tc(*args))      # the group's heads as the rows of a tensor-core tile
         return out
     check(lib.b200_diff_attn(_p(out), H * vdim, _p(q), _p(k_cache), _p(v_cache), _p(gate),
                              gate.stride(0) if gate is not None else 0, _p(q_cu), _p(kv_cu),

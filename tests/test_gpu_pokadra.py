@@ -199,7 +199,7 @@ def _attend_case(dtype, H, G, dim, vdim, window, keep, block_size, cached, n_new
 
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("H,G,dim,vdim", [(4, 2, 16, 24), (3, 3, 20, 8), (2, 1, 64, 130), (8, 2, 48, 80), (2, 2, 64, 128),
-                                          (3, 1, 32, 16), (6, 2, 128, 64), (16, 2, 16, 32)])
+                                          (3, 1, 32, 16), (6, 2, 128, 64), (16, 2, 16, 32), (2, 2, 8, 12), (5, 1, 8, 16), (34, 1, 16, 16)])
 def test_attention_window_and_kept_tokens_edges(dtype, H, G, dim, vdim):
     """Decoded rows (one new token each) and prompt rows whose loud key lies just inside / just outside the window,
     on the last kept token / the first one not kept, and far back with no window at all."""
@@ -235,6 +235,11 @@ def test_attention_first_tokens_and_block_borders(dtype):
         loud[0], loud[-1], loud[n_new // 2] = max(0, cached - win + 1) if win else 0, kp - 1 if kp else cached, 0
         got, want = _attend_case(dtype, 4, 2, 32, 48, win, kp, 16, cached, n_new, loud, seed=win + kp)
         assert float((got - want).abs().max()) < tol, (win, kp, cached, n_new)
+    # two new tokens (the single-token kernels) on caches that end just before, at and just after a 64-key tile border
+    for cached in (0, 1, 62, 63, 64, 65, 127, 128, 200):
+        for H, G in ((8, 2), (3, 3)):
+            got, want = _attend_case(dtype, H, G, 32, 48, 50, 5, 16, cached, 2, [min(cached, 4), None], seed=cached)
+            assert float((got - want).abs().max()) < tol, (cached, H, G)
     # window as long as, and longer than, the sequence; more kept tokens than the sequence has
     for win, kp in ((19, 0), (64, 0), (3, 40)):
         got, want = _attend_case(dtype, 2, 2, 8, 8, win, kp, 4, 0, 19, [None] * 19, seed=win)
