@@ -582,6 +582,15 @@ B200_API int b200_glu_clamped(void* out, const void* in, int64_t rows, int64_t n
 B200_API int b200_token_gated_gelu(void* out, const void* in, int64_t ld_in, const void* table, int64_t ld_table,
                                    int64_t col0, const int32_t* tokens, int64_t rows, int64_t n, int64_t vocab,
                                    int dtype, b200_stream_t stream);
+/* The per-token term and its post-norm in one launch, for few rows: y = P (gelu_tanh(G h) * table[tok, col0 : col0 +
+ * side_dim]) with G [side_dim, W], P [W, side_dim] and h [rows, W] of type T (intermediate results rounded to T like
+ * matrix products), then b200_postnorm_residual's arithmetic on y. */
+B200_API int b200_token_side_postnorm(float* x_out, void* h_out /*nullable*/, const float* x_in, const void* h,
+                                      const void* gate_weight, const void* proj_weight, const void* table,
+                                      int64_t ld_table, int64_t col0, const int32_t* tokens, int64_t vocab,
+                                      int64_t side_dim, const float* weight, int64_t rows, int64_t W, int64_t groups,
+                                      float mult, float eps, float* hist /*nullable*/, int64_t hist_stride,
+                                      int64_t n_hist, const float* coef /*nullable*/, int dtype, b200_stream_t stream);
 /* Minimal gated recurrent unit over each sequence's tokens of the step (see mingru.cu): proj = [z | x | g] column
  * blocks of `width`, state fp32 [n_slots, width]. */
 B200_API int b200_mingru_scan(void* out, int64_t ldo, const void* proj, int64_t ld, const float* z_bias /*nullable*/,

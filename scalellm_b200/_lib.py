@@ -125,6 +125,8 @@ SIGNATURES = {
     "b200_group_rms_norm": (_int, [_vp, _vp, _vp, _i64, _i64, _i64, _f32, _int, _vp]),
     "b200_glu_clamped": (_int, [_vp, _vp, _i64, _i64, _i64, _f32, _f32, _int, _vp]),
     "b200_token_gated_gelu": (_int, [_vp, _vp, _i64, _vp, _i64, _i64, _vp, _i64, _i64, _i64, _int, _vp]),
+    "b200_token_side_postnorm": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _vp, _i64, _i64, _vp, _i64, _i64,
+                                        _i64, _f32, _f32, _vp, _i64, _i64, _vp, _int, _vp]),
     "b200_mingru_scan": (_int, [_vp, _i64, _vp, _i64, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _int, _vp]),
     "b200_mingru_chunked_workspace_floats": (_i64, [_i64, _i64, _i64, _i64]),
     "b200_mingru_scan_chunked": (_int, [_vp, _i64, _vp, _i64, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _vp,

@@ -277,7 +277,7 @@ POKADRA_SIZES = {
                   ff=11008, side=64, buckets=100003, vocab=32000),
 }
 POKADRA_KERNELS = ["bigram_embed", "postnorm_residual", "group_rms_norm", "glu_clamped", "token_gated_gelu",
-                   "mingru_scan", "diff_attn_prepare", "diff_attn"]
+                   "token_side_postnorm", "mingru_scan", "diff_attn_prepare", "diff_attn"]
 
 
 def pokadra_config(s: dict) -> dict:

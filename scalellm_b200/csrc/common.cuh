@@ -141,6 +141,27 @@ struct Num<float> {
 
 // round-trip through T: the reference computes "in T" by converting to float,
 // doing ONE op, and rounding back (c10::BFloat16 / c10::Half operators).
+// 4 consecutive elements as floats (one 8- or 16-byte load; p aligned to that)
+template <typename T>
+__device__ __forceinline__ void load4(const T* p, float (&v)[4]);
+template <>
+__device__ __forceinline__ void load4<float>(const float* p, float (&v)[4]) {
+  const float4 x = *reinterpret_cast<const float4*>(p);
+  v[0] = x.x; v[1] = x.y; v[2] = x.z; v[3] = x.w;
+}
+template <>
+__device__ __forceinline__ void load4<__nv_bfloat16>(const __nv_bfloat16* p, float (&v)[4]) {
+  const uint2 x = *reinterpret_cast<const uint2*>(p);
+  const float2 a = Num<__nv_bfloat16>::unpack(x.x), b = Num<__nv_bfloat16>::unpack(x.y);
+  v[0] = a.x; v[1] = a.y; v[2] = b.x; v[3] = b.y;
+}
+template <>
+__device__ __forceinline__ void load4<__half>(const __half* p, float (&v)[4]) {
+  const uint2 x = *reinterpret_cast<const uint2*>(p);
+  const float2 a = Num<__half>::unpack(x.x), b = Num<__half>::unpack(x.y);
+  v[0] = a.x; v[1] = a.y; v[2] = b.x; v[3] = b.y;
+}
+
 template <typename T>
 __device__ __forceinline__ float rnd(float x) {
   return Num<T>::to_f(Num<T>::from_f(x));

@@ -87,27 +87,6 @@ diff_attn_prepare_kernel(float* __restrict__ q_out, const T* __restrict__ q_in, 
   }
 }
 
-// 4 consecutive elements of a cache row as floats (one 8- or 16-byte load)
-template <typename T>
-__device__ __forceinline__ void load4(const T* p, float (&v)[4]);
-template <>
-__device__ __forceinline__ void load4<float>(const float* p, float (&v)[4]) {
-  const float4 x = *reinterpret_cast<const float4*>(p);
-  v[0] = x.x; v[1] = x.y; v[2] = x.z; v[3] = x.w;
-}
-template <>
-__device__ __forceinline__ void load4<__nv_bfloat16>(const __nv_bfloat16* p, float (&v)[4]) {
-  const uint2 x = *reinterpret_cast<const uint2*>(p);
-  const float2 a = Num<__nv_bfloat16>::unpack(x.x), b = Num<__nv_bfloat16>::unpack(x.y);
-  v[0] = a.x; v[1] = a.y; v[2] = b.x; v[3] = b.y;
-}
-template <>
-__device__ __forceinline__ void load4<__half>(const __half* p, float (&v)[4]) {
-  const uint2 x = *reinterpret_cast<const uint2*>(p);
-  const float2 a = Num<__half>::unpack(x.x), b = Num<__half>::unpack(x.y);
-  v[0] = a.x; v[1] = a.y; v[2] = b.x; v[3] = b.y;
-}
-
 // One CTA per (row, key/value head, chunk of RH query heads of that group); warp = (head r, key split s), so the
 // RH heads' reads of the same cache rows meet in L1.  NCH: value channels per lane = 4 * NCH (lane owns channels
 // (c * 32 + lane) * 4 .. + 3 when VEC, lane + 32 * c otherwise).  VEC needs dim % 4 == 0 and vdim % 4 == 0 with
@@ -754,6 +733,8 @@ diff_attn_prefill_kernel(__nv_bfloat16* __restrict__ out, int64_t ldo, const flo
 // shared memory at the end.
 // ------------------------------------------------------------------------------------------------------------
 constexpr int kDK = 64;
+constexpr int kDS = 2;     // staged tiles: one in flight while one is consumed (a third bought nothing: the walk of a
+                           // CTA is bound by its own instruction latency, and shared memory bounds the CTAs per SM)
 
 template <int KS_MAX, int VT_MAX>
 __global__ void __launch_bounds__(128)
@@ -769,8 +750,8 @@ diff_attn_decode_tc_kernel(__nv_bfloat16* __restrict__ out, int64_t ldo, const f
   __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(smraw);     // [16][KROW]
   float* ml_s = reinterpret_cast<float*>(Qs + 16 * KROW);          // [4 warps][2 maps][2: m, l][16 rows]
   unsigned char* big = reinterpret_cast<unsigned char*>(ml_s + 4 * 2 * 2 * 16);
-  __nv_bfloat16* Ks = reinterpret_cast<__nv_bfloat16*>(big);       // [2][kDK][KROW]
-  __nv_bfloat16* Vs = Ks + 2 * kDK * KROW;                         // [2][kDK][VROW]
+  __nv_bfloat16* Ks = reinterpret_cast<__nv_bfloat16*>(big);       // [kDS][kDK][KROW]
+  __nv_bfloat16* Vs = Ks + kDS * kDK * KROW;                         // [kDS][kDK][VROW]
   float* o_s = reinterpret_cast<float*>(big);                      // after the walk: [4 warps][2 maps][16][vdim]
   (void)tile_bytes;
   const int row = blockIdx.x, g = blockIdx.y, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -809,8 +790,10 @@ diff_attn_decode_tc_kernel(__nv_bfloat16* __restrict__ out, int64_t ldo, const f
       for (int c = sub; c < vdim / 8; c += 2) cp_async16(vd + c * 8, vr + c * 8, ok);
     }
   };
-  load_tile(0, 0);
-  cp_async_commit();
+  for (int t = 0; t < kDS - 1; ++t) {
+    if (t < n_tiles) load_tile(t, t);
+    cp_async_commit();
+  }
   const int gr = lane >> 2, qc = (lane & 3) * 2;
   float mx[2][2], ls[2][2];
   float o[2][VT_MAX * 2][4];
@@ -822,10 +805,10 @@ diff_attn_decode_tc_kernel(__nv_bfloat16* __restrict__ out, int64_t ldo, const f
     for (int n = 0; n < VT_MAX * 2; ++n) o[m][n][0] = o[m][n][1] = o[m][n][2] = o[m][n][3] = 0.0f;
   }
   for (int it = 0; it < n_tiles; ++it) {
-    const int buf = it & 1;
-    cp_async_wait_all();
-    __syncthreads();
-    if (it + 1 < n_tiles) load_tile(it + 1, buf ^ 1);
+    const int buf = it % kDS;
+    asm volatile("cp.async.wait_group %0;" ::"n"(kDS - 2) : "memory");   // tile `it` has landed
+    __syncthreads();                                       // and everyone is done with tile it - 1
+    if (it + kDS - 1 < n_tiles) load_tile(it + kDS - 1, (it + kDS - 1) % kDS);
     cp_async_commit();
     const int j0 = tile_j0(it) + warp * 16;              // this warp's 16 keys of the tile
     if (j0 > i) continue;                                // all after the row's position
@@ -1164,7 +1147,7 @@ int b200_diff_attn_decode_tc(void* out, int64_t ldo, const float* q, const void*
                  "diff_attn_decode_tc: bad shape or alignment");
   auto st = static_cast<cudaStream_t>(stream);
   const int R = (int)(H / G), chunks = (R + 15) / 16;
-  const size_t tiles = ((size_t)2 * kDK * (2 * dim + 8) + (size_t)2 * kDK * (vdim + 8)) * 2;
+  const size_t tiles = ((size_t)kDS * kDK * (2 * dim + 8) + (size_t)kDS * kDK * (vdim + 8)) * 2;
   const size_t merge = (size_t)4 * 2 * 16 * vdim * sizeof(float);
   const size_t big = tiles > merge ? tiles : merge;
   const size_t smem = (size_t)16 * (2 * dim + 8) * 2 + 4 * 2 * 2 * 16 * sizeof(float) + big;

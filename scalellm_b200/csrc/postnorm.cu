@@ -41,20 +41,15 @@ __global__ void bigram_embed_kernel(float* __restrict__ x, T* __restrict__ h, co
   }
 }
 
-// one CTA per row; y is held in shared memory between the two passes; warp w owns groups w, w + 8, ...
+// The second half of a post-norm launch for one row whose sublayer result y_s [W] lies in shared memory: group
+// root mean squares (warp w owns groups w, w + 8, ...), the residual add, the history and its average.
 template <typename T>
-__global__ void __launch_bounds__(kRowThreads)
-postnorm_residual_kernel(float* __restrict__ x_out, T* __restrict__ h_out, const float* __restrict__ x_in,
-                         const T* __restrict__ y, int64_t ldy, const float* __restrict__ w, int W, int groups,
-                         float mult, float eps, float* __restrict__ hist, int64_t hist_stride, int n_hist,
-                         const float* __restrict__ coef) {
-  extern __shared__ float sm[];
-  float* y_s = sm;            // [W]
-  float* r_s = sm + W;        // [groups] reciprocal root mean squares
-  const int row = blockIdx.x;
+__device__ __forceinline__ void postnorm_tail(float* __restrict__ x_out, T* __restrict__ h_out,
+                                              const float* __restrict__ x_in, const float* y_s, float* r_s,
+                                              const float* __restrict__ w, int row, int W, int groups, float mult,
+                                              float eps, float* __restrict__ hist, int64_t hist_stride, int n_hist,
+                                              const float* __restrict__ coef) {
   const int gs = W / groups;
-  for (int i = threadIdx.x; i < W; i += kRowThreads) y_s[i] = Num<T>::to_f(y[(size_t)row * ldy + i]);
-  __syncthreads();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   for (int g = warp; g < groups; g += kRowThreads / 32) {
     float ss = 0.0f;
@@ -78,6 +73,84 @@ postnorm_residual_kernel(float* __restrict__ x_out, T* __restrict__ h_out, const
     x_out[base + i] = r;
     if (h_out) h_out[base + i] = Num<T>::from_f(r);
   }
+}
+
+// one CTA per row; y is held in shared memory between the two passes
+template <typename T>
+__global__ void __launch_bounds__(kRowThreads)
+postnorm_residual_kernel(float* __restrict__ x_out, T* __restrict__ h_out, const float* __restrict__ x_in,
+                         const T* __restrict__ y, int64_t ldy, const float* __restrict__ w, int W, int groups,
+                         float mult, float eps, float* __restrict__ hist, int64_t hist_stride, int n_hist,
+                         const float* __restrict__ coef) {
+  extern __shared__ __align__(16) float sm[];
+  float* y_s = sm;            // [W]
+  float* r_s = sm + W;        // [groups] reciprocal root mean squares
+  const int row = blockIdx.x;
+  for (int i = threadIdx.x; i < W; i += kRowThreads) y_s[i] = Num<T>::to_f(y[(size_t)row * ldy + i]);
+  __syncthreads();
+  postnorm_tail<T>(x_out, h_out, x_in, y_s, r_s, w, row, W, groups, mult, eps, hist, hist_stride, n_hist, coef);
+}
+
+// The per-token term of a layer for a few rows (decoding) in ONE launch instead of two small matrix products, the
+// gate and the post-norm: a = G h (one warp per output, rounded to T like a GEMM result), gg = gelu_tanh(a) *
+// table[tok, col0 + c], y = P gg (rounded to T), then the post-norm tail.  h: the row as the matrix products read it
+// (T; the fp32 residual itself when T is float).  G [sd, W], P [W, sd] row-major; their rows are read 4 elements a
+// load where they start on 16-byte boundaries.
+template <typename T>
+__global__ void __launch_bounds__(kRowThreads)
+token_side_postnorm_kernel(float* __restrict__ x_out, T* __restrict__ h_out, const float* __restrict__ x_in,
+                           const T* __restrict__ h, const T* __restrict__ G, const T* __restrict__ P,
+                           const T* __restrict__ table, int64_t ld_table, int col0, const int* __restrict__ tokens,
+                           int vocab, int sd, const float* __restrict__ w, int W, int groups, float mult, float eps,
+                           float* __restrict__ hist, int64_t hist_stride, int n_hist,
+                           const float* __restrict__ coef, int vec_g, int vec_p) {
+  extern __shared__ __align__(16) float sm[];
+  float* h_s = sm;                       // [W]  the input row
+  float* y_s = h_s + W;                  // [W]
+  float* g_s = y_s + W;                  // [sd rounded up to 4]
+  float* r_s = g_s + ((sd + 3) / 4) * 4; // [groups]
+  const int row = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  for (int i = threadIdx.x; i < W; i += kRowThreads) h_s[i] = Num<T>::to_f(h[(size_t)row * W + i]);
+  __syncthreads();
+  int tok = tokens[row];
+  tok = tok < 0 ? 0 : (tok >= vocab ? vocab - 1 : tok);
+  for (int c = warp; c < sd; c += kRowThreads / 32) {
+    const T* gr = G + (size_t)c * W;
+    float acc = 0.0f;
+    if (vec_g) {
+      for (int i = lane * 4; i < W; i += 128) {
+        float v[4];
+        load4<T>(gr + i, v);
+        const float4 hv = *reinterpret_cast<const float4*>(h_s + i);
+        acc += hv.x * v[0]; acc += hv.y * v[1]; acc += hv.z * v[2]; acc += hv.w * v[3];
+      }
+    } else {
+      for (int i = lane; i < W; i += 32) acc += h_s[i] * Num<T>::to_f(gr[i]);
+    }
+    acc = warp_sum(acc);
+    if (lane == 0) {
+      const float a = rnd<T>(acc);
+      const float gl = 0.5f * a * (1.0f + tanhf(0.7978845608028654f * (a + 0.044715f * a * a * a)));
+      g_s[c] = rnd<T>(gl * Num<T>::to_f(table[(int64_t)tok * ld_table + col0 + c]));
+    }
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < W; i += kRowThreads) {
+    const T* pr = P + (size_t)i * sd;
+    float acc = 0.0f;
+    if (vec_p) {
+      for (int c = 0; c < sd; c += 4) {
+        float v[4];
+        load4<T>(pr + c, v);
+        acc += g_s[c] * v[0]; acc += g_s[c + 1] * v[1]; acc += g_s[c + 2] * v[2]; acc += g_s[c + 3] * v[3];
+      }
+    } else {
+      for (int c = 0; c < sd; ++c) acc += g_s[c] * Num<T>::to_f(pr[c]);
+    }
+    y_s[i] = rnd<T>(acc);
+  }
+  __syncthreads();
+  postnorm_tail<T>(x_out, h_out, x_in, y_s, r_s, w, row, W, groups, mult, eps, hist, hist_stride, n_hist, coef);
 }
 
 // out = x / sqrt(mean_group(x^2) + eps) * w for fp32 rows x, written as T; one CTA per row
@@ -196,6 +269,38 @@ int b200_postnorm_residual(float* x_out, void* h_out, const float* x_in, const v
         eps, hist, hist_stride, (int)n_hist, coef);
   });
   B200_LAUNCH_OK("postnorm_residual_kernel");
+  return B200_OK;
+}
+
+int b200_token_side_postnorm(float* x_out, void* h_out, const float* x_in, const void* h, const void* gate_weight,
+                             const void* proj_weight, const void* table, int64_t ld_table, int64_t col0,
+                             const int32_t* tokens, int64_t vocab, int64_t side_dim, const float* weight,
+                             int64_t rows, int64_t W, int64_t groups, float mult, float eps, float* hist,
+                             int64_t hist_stride, int64_t n_hist, const float* coef, int dtype,
+                             b200_stream_t stream) {
+  if (rows == 0) return B200_OK;
+  B200_CHECK_ARG(x_out && x_in && h && gate_weight && proj_weight && table && tokens && weight,
+                 "token_side_postnorm: null pointer");
+  B200_CHECK_ARG(rows > 0 && W > 0 && groups > 0 && W % groups == 0 && side_dim > 0 && vocab > 0 && col0 >= 0 &&
+                     ld_table >= col0 + side_dim && (2 * W + groups + side_dim + 4) * 4 <= 200 * 1024,
+                 "token_side_postnorm: bad shape");
+  B200_CHECK_ARG(!hist || (n_hist > 0 && coef && hist_stride >= rows * W), "token_side_postnorm: bad history");
+  auto st = static_cast<cudaStream_t>(stream);
+  const size_t smem = (size_t)(2 * W + groups + side_dim + 4) * sizeof(float);
+  const int esz = dtype == B200_FP32 ? 4 : 2;
+  // 4 elements a load: every row of G (W elements) and of P (side_dim elements) starts on a 4-element boundary
+  const int vec_g = W % 4 == 0 && is_aligned(gate_weight, 16) && (W * esz) % (4 * esz) == 0;
+  const int vec_p = side_dim % 4 == 0 && is_aligned(proj_weight, 16);
+  POSTNORM_DISPATCH(dtype, {
+    if (smem > 48 * 1024)
+      B200_CUDA_OK(cudaFuncSetAttribute(token_side_postnorm_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                        (int)smem));
+    token_side_postnorm_kernel<T><<<(unsigned)rows, kRowThreads, smem, st>>>(
+        x_out, static_cast<T*>(h_out), x_in, static_cast<const T*>(h), static_cast<const T*>(gate_weight),
+        static_cast<const T*>(proj_weight), static_cast<const T*>(table), ld_table, (int)col0, tokens, (int)vocab,
+        (int)side_dim, weight, (int)W, (int)groups, mult, eps, hist, hist_stride, (int)n_hist, coef, vec_g, vec_p);
+  });
+  B200_LAUNCH_OK("token_side_postnorm_kernel");
   return B200_OK;
 }
 

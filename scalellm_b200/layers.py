@@ -885,13 +885,24 @@ class ClampedGLU:
 
 class TokenSideInput:
     """A per-token, per-layer learned vector e = table[token, col0 : col0 + dim] gates a narrow projection of the
-    residual: y = P (gelu_tanh(G h) * e).  (The caller normalises y and adds it.)"""
+    residual: y = P (gelu_tanh(G h) * e), which enters the residual through a PostNormResidual.  Steps of at most
+    FUSED_ROWS rows run gate, projection and post-norm as one launch."""
 
-    def __init__(self, table: torch.Tensor, col0: int, gate: torch.Tensor, proj: torch.Tensor):
-        self.table, self.col0 = table, col0
+    FUSED_ROWS = 64
+
+    def __init__(self, table: torch.Tensor, col0: int, gate: torch.Tensor, proj: torch.Tensor, norm: PostNormResidual):
+        self.table, self.col0, self.norm = table, col0, norm
         self.gate, self.proj = Linear(gate), Linear(proj)
 
-    def forward(self, h: torch.Tensor, tokens: torch.Tensor) -> torch.Tensor:
-        return self.proj(kernels.token_gated_gelu(self.gate(h), self.table, self.col0, tokens))
+    def forward(self, x: torch.Tensor, h: torch.Tensor, tokens: torch.Tensor, x_out: Optional[torch.Tensor] = None,
+                hist: Optional[torch.Tensor] = None, n_hist: int = 0, coef: Optional[torch.Tensor] = None):
+        """x: fp32 residual, h: the same rows as the matrix products read them.  Returns (new x, new h)."""
+        n = self.norm
+        if x.shape[0] <= self.FUSED_ROWS:
+            out, hh = kernels.token_side_postnorm(x, h, self.gate.weight, self.proj.weight, self.table, self.col0,
+                                                  tokens, n.weight, n.groups, n.mult, n.eps, hist, n_hist, coef, x_out)
+            return out, (hh if hh is not None else out)
+        y = self.proj(kernels.token_gated_gelu(self.gate(h), self.table, self.col0, tokens))
+        return n(x, y, x_out=x_out, hist=hist, n_hist=n_hist, coef=coef)
 
     __call__ = forward

@@ -122,7 +122,6 @@ class _Layer:
     ff = None
     norm2: Optional[PostNormResidual] = None
     side: Optional[TokenSideInput] = None
-    side_norm: Optional[PostNormResidual] = None
     dwa: Optional[torch.Tensor] = None
     cache: Optional[KVCache] = None       # this layer's own, or the one of the layer it takes keys and values from
     kv_from: Optional[int] = None
@@ -202,8 +201,8 @@ class PokadraDecoder:
                 lay.norm2 = PostNormResidual(f32(p + "norm2"), self.groups, self.mult, eps)
             if side_cfg:
                 sd = int(side_cfg["dim"])
-                lay.side = TokenSideInput(side_table, i * sd, w(p + "side.gate"), w(p + "side.proj"))
-                lay.side_norm = PostNormResidual(f32(p + "side.norm"), 1, self.mult, eps)
+                lay.side = TokenSideInput(side_table, i * sd, w(p + "side.gate"), w(p + "side.proj"),
+                                          PostNormResidual(f32(p + "side.norm"), 1, self.mult, eps))
             if p + "dwa" in tensors:
                 lay.dwa = f32(p + "dwa")
             self.layers.append(lay)
@@ -238,22 +237,23 @@ class PokadraDecoder:
             if lay.ff is not None:
                 subs.append(("ff", lay.norm2))
             if lay.side is not None:
-                subs.append(("side", lay.side_norm))
+                subs.append(("side", None))
             for n, (kind, norm) in enumerate(subs):
+                kw = {"x_out": work}
+                if n == len(subs) - 1 and hist is not None:
+                    if lay.dwa is not None:
+                        kw = {"x_out": work, "hist": hist, "n_hist": i + 2, "coef": lay.dwa}
+                    else:       # no average after this layer: its result goes on and into the history
+                        kw = {"x_out": hist[i + 1]}
+                if kind == "side":
+                    x, h = lay.side(x, h, tokens, **kw)
+                    continue
                 if kind == "mix":
                     y = (lay.mixer(h, positions, lay.cache, params) if lay.kind == "attention"
                          else lay.mixer(h, positions, params))
-                elif kind == "ff":
+                else:
                     y = lay.ff(h)
-                else:
-                    y = lay.side(h, tokens)
-                if n == len(subs) - 1 and hist is not None:
-                    if lay.dwa is not None:
-                        x, h = norm(x, y, x_out=work, hist=hist, n_hist=i + 2, coef=lay.dwa)
-                    else:       # no average after this layer: its result goes on and into the history
-                        x, h = norm(x, y, x_out=hist[i + 1])
-                else:
-                    x, h = norm(x, y, x_out=work)
+                x, h = norm(x, y, **kw)
             if layer_out is not None:
                 layer_out.append(x.clone())
         if last_token_idxes is not None:

@@ -128,6 +128,41 @@ def test_clamped_glu_and_token_gate():
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("W,sd,groups", [(64, 8, 1), (200, 12, 4), (48, 1, 3)])
+def test_per_token_term_in_one_launch(dtype, W, sd, groups):
+    """Gate, projection and post-norm of the per-token term as one kernel, with and without the history."""
+    from scalellm_b200 import kernels
+    g = torch.Generator().manual_seed(W + sd)
+    rows, V, layer, n = 5, 23, 2, 3
+    x = torch.randn(rows, W, generator=g)
+    G_, P_ = (torch.randn(sd, W, generator=g) / math.sqrt(W)).to(dtype), torch.randn(W, sd, generator=g).to(dtype)
+    table, wn = torch.randn(V, 4 * sd, generator=g).to(dtype), torch.randn(W, generator=g)
+    tok = [3, 22, 0, 3, 9]
+    h = x.to(dtype)
+    w = {"side.embed": table.double(), "l2.side.gate": G_.double(), "l2.side.proj": P_.double(),
+         "l2.side.norm": torch.ones(W, dtype=torch.float64)}
+    e = table.double()[tok, layer * sd:(layer + 1) * sd]
+    y = (op.gelu_tanh(h.double() @ G_.double().T) * e) @ P_.double().T
+    ref = x.double() + 0.4 * op.group_norm(y, wn.double(), groups, 1e-5)
+    tol = 1e-4 if dtype == torch.float32 else 0.06
+    out, hh = kernels.token_side_postnorm(x.to(DEV), h.to(DEV), G_.to(DEV), P_.to(DEV), table.to(DEV), layer * sd,
+                                          torch.tensor(tok, dtype=torch.int32, device=DEV), wn.to(DEV), groups, 0.4,
+                                          1e-5, x_out=torch.empty(rows, W, device=DEV))
+    assert float((out.cpu().double() - ref).abs().max()) < tol * (1 + float(ref.abs().max()))
+    assert (hh is None) == (dtype == torch.float32)
+    hist = torch.randn(n + 1, rows, W, generator=g)
+    coef = torch.randn(n, generator=g)
+    hd = hist.to(DEV)
+    out, _ = kernels.token_side_postnorm(x.to(DEV), h.to(DEV), G_.to(DEV), P_.to(DEV), table.to(DEV), layer * sd,
+                                         torch.tensor(tok, dtype=torch.int32, device=DEV), wn.to(DEV), groups, 0.4,
+                                         1e-5, hd, n, coef.to(DEV), torch.empty(rows, W, device=DEV))
+    avg = sum(coef[j].double() * (ref if j == n - 1 else hist[j].double()) for j in range(n))
+    assert float((out.cpu().double() - avg).abs().max()) < tol * (1 + float(avg.abs().max()))
+    assert float((hd[n - 1].cpu().double() - ref).abs().max()) < tol * (1 + float(ref.abs().max()))
+    assert torch.equal(hd[n].cpu(), hist[n])
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("width", [1, 40, 300])
 def test_mingru_in_portions_from_a_dirty_slot(dtype, width):
     """One sequence in portions of 33 / 2 / 1 / 1 / 30 beside a second one that starts later, slots not cleared."""
