@@ -583,7 +583,7 @@ B200_API int b200_token_gated_gelu(void* out, const void* in, int64_t ld_in, con
                                    int64_t col0, const int32_t* tokens, int64_t rows, int64_t n, int64_t vocab,
                                    int dtype, b200_stream_t stream);
 /* The per-token term and its post-norm in one launch, for few rows: y = P (gelu_tanh(G h) * table[tok, col0 : col0 +
- * side_dim]) with G [side_dim, W], P [W, side_dim] and h [rows, W] of type T (intermediate results rounded to T like
+ * side_dim]) with G [side_dim, W], P given TRANSPOSED as [side_dim, W], and h [rows, W] of type T (intermediate results rounded to T like
  * matrix products), then b200_postnorm_residual's arithmetic on y. */
 B200_API int b200_token_side_postnorm(float* x_out, void* h_out /*nullable*/, const float* x_in, const void* h,
                                       const void* gate_weight, const void* proj_weight, const void* table,

@@ -17,6 +17,7 @@ namespace b200 {
 namespace {
 
 constexpr int kRowThreads = 256;
+constexpr int kSideThreads = 1024;   // the one-launch per-token term: one CTA streams two matrices, it needs the loads in flight
 
 template <typename T>
 __global__ void bigram_embed_kernel(float* __restrict__ x, T* __restrict__ h, const T* __restrict__ table,
@@ -51,7 +52,7 @@ __device__ __forceinline__ void postnorm_tail(float* __restrict__ x_out, T* __re
                                               const float* __restrict__ coef) {
   const int gs = W / groups;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  for (int g = warp; g < groups; g += kRowThreads / 32) {
+  for (int g = warp; g < groups; g += (int)blockDim.x / 32) {
     float ss = 0.0f;
     for (int i = lane; i < gs; i += 32) {
       const float v = y_s[g * gs + i];
@@ -62,7 +63,7 @@ __device__ __forceinline__ void postnorm_tail(float* __restrict__ x_out, T* __re
   }
   __syncthreads();
   const size_t base = (size_t)row * W;
-  for (int i = threadIdx.x; i < W; i += kRowThreads) {
+  for (int i = threadIdx.x; i < W; i += (int)blockDim.x) {
     float r = x_in[base + i] + mult * (y_s[i] * r_s[i / gs] * w[i]);
     if (hist) {
       hist[(size_t)(n_hist - 1) * hist_stride + base + i] = r;
@@ -94,10 +95,10 @@ postnorm_residual_kernel(float* __restrict__ x_out, T* __restrict__ h_out, const
 // The per-token term of a layer for a few rows (decoding) in ONE launch instead of two small matrix products, the
 // gate and the post-norm: a = G h (one warp per output, rounded to T like a GEMM result), gg = gelu_tanh(a) *
 // table[tok, col0 + c], y = P gg (rounded to T), then the post-norm tail.  h: the row as the matrix products read it
-// (T; the fp32 residual itself when T is float).  G [sd, W], P [W, sd] row-major; their rows are read 4 elements a
-// load where they start on 16-byte boundaries.
+// (T; the fp32 residual itself when T is float).  G [sd, W] and P TRANSPOSED [sd, W], row-major; rows are read 4
+// elements a load where W is a multiple of 4 and the matrices start on 16-byte boundaries.
 template <typename T>
-__global__ void __launch_bounds__(kRowThreads)
+__global__ void __launch_bounds__(kSideThreads)
 token_side_postnorm_kernel(float* __restrict__ x_out, T* __restrict__ h_out, const float* __restrict__ x_in,
                            const T* __restrict__ h, const T* __restrict__ G, const T* __restrict__ P,
                            const T* __restrict__ table, int64_t ld_table, int col0, const int* __restrict__ tokens,
@@ -110,44 +111,70 @@ token_side_postnorm_kernel(float* __restrict__ x_out, T* __restrict__ h_out, con
   float* g_s = y_s + W;                  // [sd rounded up to 4]
   float* r_s = g_s + ((sd + 3) / 4) * 4; // [groups]
   const int row = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  for (int i = threadIdx.x; i < W; i += kRowThreads) h_s[i] = Num<T>::to_f(h[(size_t)row * W + i]);
+  for (int i = threadIdx.x; i < W; i += kSideThreads) h_s[i] = Num<T>::to_f(h[(size_t)row * W + i]);
   __syncthreads();
   int tok = tokens[row];
   tok = tok < 0 ? 0 : (tok >= vocab ? vocab - 1 : tok);
-  for (int c = warp; c < sd; c += kRowThreads / 32) {
-    const T* gr = G + (size_t)c * W;
-    float acc = 0.0f;
+  // a warp takes up to 8 of the sd outputs at a time (c = warp + 8 k): 8 independent loads per step of the row
+  constexpr int NW = kSideThreads / 32;
+  for (int c0 = warp; c0 < sd; c0 += NW * 8) {
+    float acc[8];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) acc[k] = 0.0f;
     if (vec_g) {
       for (int i = lane * 4; i < W; i += 128) {
-        float v[4];
-        load4<T>(gr + i, v);
         const float4 hv = *reinterpret_cast<const float4*>(h_s + i);
-        acc += hv.x * v[0]; acc += hv.y * v[1]; acc += hv.z * v[2]; acc += hv.w * v[3];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          const int c = c0 + k * NW;
+          if (c < sd) {
+            float v[4];
+            load4<T>(G + (size_t)c * W + i, v);
+            acc[k] += hv.x * v[0]; acc[k] += hv.y * v[1]; acc[k] += hv.z * v[2]; acc[k] += hv.w * v[3];
+          }
+        }
       }
     } else {
-      for (int i = lane; i < W; i += 32) acc += h_s[i] * Num<T>::to_f(gr[i]);
+      for (int i = lane; i < W; i += 32) {
+        const float hv = h_s[i];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          const int c = c0 + k * NW;
+          if (c < sd) acc[k] += hv * Num<T>::to_f(G[(size_t)c * W + i]);
+        }
+      }
     }
-    acc = warp_sum(acc);
-    if (lane == 0) {
-      const float a = rnd<T>(acc);
-      const float gl = 0.5f * a * (1.0f + tanhf(0.7978845608028654f * (a + 0.044715f * a * a * a)));
-      g_s[c] = rnd<T>(gl * Num<T>::to_f(table[(int64_t)tok * ld_table + col0 + c]));
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      const int c = c0 + k * NW;
+      const float sum = warp_sum(acc[k]);
+      if (lane == 0 && c < sd) {
+        const float a = rnd<T>(sum);
+        const float gl = 0.5f * a * (1.0f + tanhf(0.7978845608028654f * (a + 0.044715f * a * a * a)));
+        g_s[c] = rnd<T>(gl * Num<T>::to_f(table[(int64_t)tok * ld_table + col0 + c]));
+      }
     }
   }
   __syncthreads();
-  for (int i = threadIdx.x; i < W; i += kRowThreads) {
-    const T* pr = P + (size_t)i * sd;
-    float acc = 0.0f;
-    if (vec_p) {
-      for (int c = 0; c < sd; c += 4) {
+  // P is given transposed, [sd, W]: neighbouring threads read neighbouring outputs' weights
+  if (vec_p) {
+    for (int i = threadIdx.x * 4; i < W; i += kSideThreads * 4) {
+      float a0 = 0.0f, a1 = 0.0f, a2 = 0.0f, a3 = 0.0f;
+#pragma unroll 8
+      for (int c = 0; c < sd; ++c) {
         float v[4];
-        load4<T>(pr + c, v);
-        acc += g_s[c] * v[0]; acc += g_s[c + 1] * v[1]; acc += g_s[c + 2] * v[2]; acc += g_s[c + 3] * v[3];
+        load4<T>(P + (size_t)c * W + i, v);
+        const float gc = g_s[c];
+        a0 += gc * v[0]; a1 += gc * v[1]; a2 += gc * v[2]; a3 += gc * v[3];
       }
-    } else {
-      for (int c = 0; c < sd; ++c) acc += g_s[c] * Num<T>::to_f(pr[c]);
+      y_s[i] = rnd<T>(a0); y_s[i + 1] = rnd<T>(a1); y_s[i + 2] = rnd<T>(a2); y_s[i + 3] = rnd<T>(a3);
     }
-    y_s[i] = rnd<T>(acc);
+  } else {
+    for (int i = threadIdx.x; i < W; i += kSideThreads) {
+      float acc = 0.0f;
+      for (int c = 0; c < sd; ++c) acc += g_s[c] * Num<T>::to_f(P[(size_t)c * W + i]);
+      y_s[i] = rnd<T>(acc);
+    }
   }
   __syncthreads();
   postnorm_tail<T>(x_out, h_out, x_in, y_s, r_s, w, row, W, groups, mult, eps, hist, hist_stride, n_hist, coef);
@@ -288,14 +315,14 @@ int b200_token_side_postnorm(float* x_out, void* h_out, const float* x_in, const
   auto st = static_cast<cudaStream_t>(stream);
   const size_t smem = (size_t)(2 * W + groups + side_dim + 4) * sizeof(float);
   const int esz = dtype == B200_FP32 ? 4 : 2;
-  // 4 elements a load: every row of G (W elements) and of P (side_dim elements) starts on a 4-element boundary
+  // 4 elements a load: every row of G and of the transposed P (W elements each) starts on a 4-element boundary
   const int vec_g = W % 4 == 0 && is_aligned(gate_weight, 16) && (W * esz) % (4 * esz) == 0;
-  const int vec_p = side_dim % 4 == 0 && is_aligned(proj_weight, 16);
+  const int vec_p = W % 4 == 0 && is_aligned(proj_weight, 16);
   POSTNORM_DISPATCH(dtype, {
     if (smem > 48 * 1024)
       B200_CUDA_OK(cudaFuncSetAttribute(token_side_postnorm_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                         (int)smem));
-    token_side_postnorm_kernel<T><<<(unsigned)rows, kRowThreads, smem, st>>>(
+    token_side_postnorm_kernel<T><<<(unsigned)rows, kSideThreads, smem, st>>>(
         x_out, static_cast<T*>(h_out), x_in, static_cast<const T*>(h), static_cast<const T*>(gate_weight),
         static_cast<const T*>(proj_weight), static_cast<const T*>(table), ld_table, (int)col0, tokens, (int)vocab,
         (int)side_dim, weight, (int)W, (int)groups, mult, eps, hist, hist_stride, (int)n_hist, coef, vec_g, vec_p);

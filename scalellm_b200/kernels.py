@@ -953,25 +953,26 @@ def token_gated_gelu(a: torch.Tensor, table: torch.Tensor, col0: int, tokens: to
 # ---------------------------------------------------------------------------
 # minimal gated recurrent unit (csrc/mingru.cu)
 # ---------------------------------------------------------------------------
-def token_side_postnorm(x: torch.Tensor, h: torch.Tensor, gate_w: torch.Tensor, proj_w: torch.Tensor,
+def token_side_postnorm(x: torch.Tensor, h: torch.Tensor, gate_w: torch.Tensor, proj_wt: torch.Tensor,
                         table: torch.Tensor, col0: int, tokens: torch.Tensor, weight: torch.Tensor, groups: int,
                         mult: float, eps: float, hist: Optional[torch.Tensor] = None, n_hist: int = 0,
                         coef: Optional[torch.Tensor] = None, x_out: Optional[torch.Tensor] = None):
-    """postnorm_residual(x, P (gelu_tanh(G h) * table[tokens, col0 : col0 + sd]), ...) in one launch (few rows)."""
-    _cuda(x, h, gate_w, proj_w, table, tokens, weight, hist, coef)
+    """postnorm_residual(x, P (gelu_tanh(G h) * table[tokens, col0 : col0 + sd]), ...) in one launch (few rows).
+    proj_wt: the projection weight transposed, [sd, W]."""
+    _cuda(x, h, gate_w, proj_wt, table, tokens, weight, hist, coef)
     _f32(x, weight, hist, coef)
     _check_i32(tokens)
     rows, W = x.shape
     sd = gate_w.shape[0]
-    assert h.shape == (rows, W) and h.is_contiguous() and gate_w.shape == (sd, W) and proj_w.shape == (W, sd)
-    assert gate_w.is_contiguous() and proj_w.is_contiguous() and table.stride(1) == 1
-    assert h.dtype == gate_w.dtype == proj_w.dtype == table.dtype
+    assert h.shape == (rows, W) and h.is_contiguous() and gate_w.shape == (sd, W) and proj_wt.shape == (sd, W)
+    assert gate_w.is_contiguous() and proj_wt.is_contiguous() and table.stride(1) == 1
+    assert h.dtype == gate_w.dtype == proj_wt.dtype == table.dtype
     out = x if x_out is None else x_out
     _f32(out)
     assert hist is None or (hist.dim() == 3 and hist.shape[1:] == (rows, W) and 0 < n_hist <= hist.shape[0]
                             and coef is not None and coef.numel() >= n_hist)
     hh = torch.empty((rows, W), dtype=h.dtype, device=x.device) if h.dtype != torch.float32 else None
-    check(_lib.load().b200_token_side_postnorm(_p(out), _p(hh), _p(x), _p(h), _p(gate_w), _p(proj_w), _p(table),
+    check(_lib.load().b200_token_side_postnorm(_p(out), _p(hh), _p(x), _p(h), _p(gate_w), _p(proj_wt), _p(table),
                                                table.stride(0), col0, _p(tokens), table.shape[0], sd, _p(weight),
                                                rows, W, groups, mult, eps, _p(hist),
                                                rows * W if hist is not None else 0, n_hist, _p(coef), _dt(h),

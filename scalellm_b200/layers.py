@@ -893,13 +893,14 @@ class TokenSideInput:
     def __init__(self, table: torch.Tensor, col0: int, gate: torch.Tensor, proj: torch.Tensor, norm: PostNormResidual):
         self.table, self.col0, self.norm = table, col0, norm
         self.gate, self.proj = Linear(gate), Linear(proj)
+        self.proj_t = proj.t().contiguous()       # [dim, W]: the one-launch form reads it along W
 
     def forward(self, x: torch.Tensor, h: torch.Tensor, tokens: torch.Tensor, x_out: Optional[torch.Tensor] = None,
                 hist: Optional[torch.Tensor] = None, n_hist: int = 0, coef: Optional[torch.Tensor] = None):
         """x: fp32 residual, h: the same rows as the matrix products read them.  Returns (new x, new h)."""
         n = self.norm
         if x.shape[0] <= self.FUSED_ROWS:
-            out, hh = kernels.token_side_postnorm(x, h, self.gate.weight, self.proj.weight, self.table, self.col0,
+            out, hh = kernels.token_side_postnorm(x, h, self.gate.weight, self.proj_t, self.table, self.col0,
                                                   tokens, n.weight, n.groups, n.mult, n.eps, hist, n_hist, coef, x_out)
             return out, (hh if hh is not None else out)
         y = self.proj(kernels.token_gated_gelu(self.gate(h), self.table, self.col0, tokens))

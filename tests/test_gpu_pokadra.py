@@ -145,7 +145,7 @@ def test_per_token_term_in_one_launch(dtype, W, sd, groups):
     y = (op.gelu_tanh(h.double() @ G_.double().T) * e) @ P_.double().T
     ref = x.double() + 0.4 * op.group_norm(y, wn.double(), groups, 1e-5)
     tol = 1e-4 if dtype == torch.float32 else 0.06
-    out, hh = kernels.token_side_postnorm(x.to(DEV), h.to(DEV), G_.to(DEV), P_.to(DEV), table.to(DEV), layer * sd,
+    out, hh = kernels.token_side_postnorm(x.to(DEV), h.to(DEV), G_.to(DEV), P_.t().contiguous().to(DEV), table.to(DEV), layer * sd,
                                           torch.tensor(tok, dtype=torch.int32, device=DEV), wn.to(DEV), groups, 0.4,
                                           1e-5, x_out=torch.empty(rows, W, device=DEV))
     assert float((out.cpu().double() - ref).abs().max()) < tol * (1 + float(ref.abs().max()))
@@ -153,7 +153,7 @@ def test_per_token_term_in_one_launch(dtype, W, sd, groups):
     hist = torch.randn(n + 1, rows, W, generator=g)
     coef = torch.randn(n, generator=g)
     hd = hist.to(DEV)
-    out, _ = kernels.token_side_postnorm(x.to(DEV), h.to(DEV), G_.to(DEV), P_.to(DEV), table.to(DEV), layer * sd,
+    out, _ = kernels.token_side_postnorm(x.to(DEV), h.to(DEV), G_.to(DEV), P_.t().contiguous().to(DEV), table.to(DEV), layer * sd,
                                          torch.tensor(tok, dtype=torch.int32, device=DEV), wn.to(DEV), groups, 0.4,
                                          1e-5, hd, n, coef.to(DEV), torch.empty(rows, W, device=DEV))
     avg = sum(coef[j].double() * (ref if j == n - 1 else hist[j].double()) for j in range(n))
