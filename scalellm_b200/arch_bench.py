@@ -129,7 +129,7 @@ def _run_model(config: dict, batch: int, seqlen: int, warmup: int, steps: int, k
     # per-kernel device time of one prompt step and one decode step
     timer = KernelTimer()
     timer.wrap(kernels, kernel_names)
-    timer.wrap(kernels, ["dense_gemm"], lambda n: "linear (dense GEMMs)")
+    timer.wrap(kernels, ["dense_gemm", "dense_gemm_splitk"], lambda n: "linear (dense GEMMs)")
     timer.wrap(torch.nn.functional, ["linear"], lambda n: "linear (dense GEMMs)")
     timer.wrap(torch, ["bmm"], lambda n: "bmm (per-head key / value maps)")
     try:
@@ -153,7 +153,8 @@ def _run_model(config: dict, batch: int, seqlen: int, warmup: int, steps: int, k
 KIGALIX_KERNELS = ["embed_streams", "hc_norm", "token_shift", "gated_hc_update", "gated_act", "heads_to_rows",
                    "latent_prepare", "latent_attn", "delta_rule", "moe_route", "moe_plan", "grouped_gemm", "moe_combine"]
 LLAMA_KERNELS = ["rms_norm", "rms_norm_residual", "rope_and_set_kv_cache", "paged_kv_varlen_mha", "silu_mul",
-                 "silu_with_mul", "apply_rotary_pos_emb", "set_kv_cache"]
+                 "silu_with_mul", "apply_rotary_pos_emb", "set_kv_cache", "rms_norm_residual_splitk", "silu_mul_splitk",
+                 "rope_and_set_kv_cache_splitk"]
 
 
 def rooflines(s: dict, batch: int, seqlen: int, k: dict, l: dict, peaks: dict) -> dict:
@@ -353,7 +354,7 @@ def pokadra_rooflines(s: dict, batch: int, seqlen: int, k: dict, l: dict, peaks:
             km.get("postnorm_residual", 0.0),
             rows * W * (n_post * (4 + 4 + 2 + 2) + sum(4 * (i + 2) for i in range(s["layers"]))), 0, hbm, tf)
         out[f"llama rms_norm_residual {phase}"] = _frac(
-            lm.get("rms_norm_residual", 0.0) + lm.get("rms_norm", 0.0), rows * W * (2 * s["layers"] + 1) * 4 * 2, 0, hbm, tf)
+            lm.get("rms_norm_residual", 0.0) + lm.get("rms_norm", 0.0) + lm.get("rms_norm_residual_splitk", 0.0), rows * W * (2 * s["layers"] + 1) * 4 * 2, 0, hbm, tf)
         pw = (n_gru * 4 * s["gru"] * W + n_at * ((2 * H * dim + H * vd + H) * W) + (G * (2 * dim + vd)) * W * (n_at + 1) // 2
               + s["layers"] * (3 * s["ff"] * W + 2 * s["side"] * W))
         nlog = batch
