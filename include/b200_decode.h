@@ -572,6 +572,19 @@ B200_API int b200_postnorm_residual(float* x_out, void* h_out /*nullable*/, cons
                                     int64_t ldy, const float* weight, int64_t rows, int64_t W, int64_t groups,
                                     float mult, float eps, float* hist /*nullable*/, int64_t hist_stride,
                                     int64_t n_hist, const float* coef /*nullable*/, int dtype, b200_stream_t stream);
+/* The partition b200_dense_gemm_splitk uses for an [N, K] weight, as six integers a fused consumer is given
+ * (returns the number of partial slots, 0 if the shape has no such partition). */
+B200_API int b200_dense_splitk_plan(int64_t N, int64_t K, int32_t* plan6);
+/* b200_postnorm_residual / b200_glu_clamped fed by the split-K partials [n_slots][rows][W or 2 n] of the matrix
+ * product that made their input (its reduction pass folded in: the sum is rounded to T first). */
+B200_API int b200_postnorm_residual_splitk(float* x_out, void* h_out /*nullable*/, const float* x_in,
+                                           const float* partials, int64_t n_slots, const int32_t* plan6,
+                                           const float* weight, int64_t rows, int64_t W, int64_t groups, float mult,
+                                           float eps, float* hist /*nullable*/, int64_t hist_stride, int64_t n_hist,
+                                           const float* coef /*nullable*/, int dtype, b200_stream_t stream);
+B200_API int b200_glu_clamped_splitk(void* out, const float* partials, int64_t n_slots, const int32_t* plan6,
+                                     int64_t rows, int64_t n, float limit, float slope, int dtype,
+                                     b200_stream_t stream);
 /* out (T) = x / sqrt(mean_group(x^2) + eps) * weight for fp32 rows x [rows, W]. */
 B200_API int b200_group_rms_norm(void* out, const float* x, const float* weight, int64_t rows, int64_t W,
                                  int64_t groups, float eps, int dtype, b200_stream_t stream);

@@ -122,6 +122,10 @@ SIGNATURES = {
     "b200_bigram_embed": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i64, _f32, _int, _vp]),
     "b200_postnorm_residual": (_int, [_vp, _vp, _vp, _vp, _i64, _vp, _i64, _i64, _i64, _f32, _f32, _vp, _i64, _i64,
                                       _vp, _int, _vp]),
+    "b200_dense_splitk_plan": (_int, [_i64, _i64, _vp]),
+    "b200_postnorm_residual_splitk": (_int, [_vp, _vp, _vp, _vp, _i64, _vp, _vp, _i64, _i64, _i64, _f32, _f32, _vp, _i64,
+                                             _i64, _vp, _int, _vp]),
+    "b200_glu_clamped_splitk": (_int, [_vp, _vp, _i64, _vp, _i64, _i64, _f32, _f32, _int, _vp]),
     "b200_group_rms_norm": (_int, [_vp, _vp, _vp, _i64, _i64, _i64, _f32, _int, _vp]),
     "b200_glu_clamped": (_int, [_vp, _vp, _i64, _i64, _i64, _f32, _f32, _int, _vp]),
     "b200_token_gated_gelu": (_int, [_vp, _vp, _i64, _vp, _i64, _i64, _vp, _i64, _i64, _i64, _int, _vp]),

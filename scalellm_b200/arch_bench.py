@@ -281,8 +281,9 @@ POKADRA_SIZES = {
     "w4096": dict(width=4096, layers=4, heads=32, kv_heads=8, dim=64, vdim=128, window=512, keep=4, gru=5120,
                   ff=11008, side=64, buckets=100003, vocab=32000),
 }
-POKADRA_KERNELS = ["bigram_embed", "postnorm_residual", "group_rms_norm", "glu_clamped", "token_gated_gelu",
-                   "token_side_postnorm", "mingru_scan", "diff_attn_prepare", "diff_attn"]
+POKADRA_KERNELS = ["bigram_embed", "postnorm_residual", "postnorm_residual_splitk", "group_rms_norm", "glu_clamped",
+                   "glu_clamped_splitk", "token_gated_gelu", "token_side_postnorm", "mingru_scan", "diff_attn_prepare",
+                   "diff_attn"]
 
 
 def pokadra_config(s: dict) -> dict:

@@ -345,6 +345,13 @@ int b200_dense_splitk_splits(int64_t M, int64_t N, int64_t K) {
   return w4_get_plan(N, K, 128).slots;
 }
 
+int b200_dense_splitk_plan(int64_t N, int64_t K, int32_t* plan6) {
+  if (!plan6 || N <= 0 || K <= 0 || N % 128 || K % 128) return 0;
+  const W4Plan pl = w4_get_plan(N, K, 128);
+  plan6[0] = pl.units; plan6[1] = pl.P; plan6[2] = pl.KT; plan6[3] = pl.NT; plan6[4] = pl.slots; plan6[5] = pl.nsub_log2;
+  return pl.slots;
+}
+
 int b200_dense_gemm_splitk(float* partials, const void* A, const void* W, int64_t M, int64_t N,
                            int64_t K, int64_t lda, int64_t ldw, int splits, b200_stream_t stream) {
   B200_CHECK_ARG(partials && A && W, "dense_gemm_splitk: null pointer");

@@ -92,6 +92,31 @@ postnorm_residual_kernel(float* __restrict__ x_out, T* __restrict__ h_out, const
   postnorm_tail<T>(x_out, h_out, x_in, y_s, r_s, w, row, W, groups, mult, eps, hist, hist_stride, n_hist, coef);
 }
 
+// The same launch fed by the split-K partials of the matrix product that made y (fp32 [slots][rows][W], the
+// contributing slots of a column group given by the product's partition): their sum is rounded to T, which is what
+// the product's own reduction pass would have stored, so the reduction costs no launch of its own.
+template <typename T>
+__global__ void __launch_bounds__(kRowThreads)
+postnorm_residual_splitk_kernel(float* __restrict__ x_out, T* __restrict__ h_out, const float* __restrict__ x_in,
+                                const float* __restrict__ partials, W4Plan plan, int64_t slot_stride,
+                                const float* __restrict__ w, int W, int groups, float mult, float eps,
+                                float* __restrict__ hist, int64_t hist_stride, int n_hist,
+                                const float* __restrict__ coef) {
+  extern __shared__ __align__(16) float sm[];
+  float* y_s = sm;
+  float* r_s = sm + W;
+  const int row = blockIdx.x;
+  const float* prow = partials + (size_t)row * W;
+  for (int v = threadIdx.x; v < W / 8; v += kRowThreads) {
+    float a[8];
+    w4_sum_partials8(a, prow + v * 8, slot_stride, w4_contrib_col(plan, v * 8));
+#pragma unroll
+    for (int i = 0; i < 8; ++i) y_s[v * 8 + i] = rnd<T>(a[i]);
+  }
+  __syncthreads();
+  postnorm_tail<T>(x_out, h_out, x_in, y_s, r_s, w, row, W, groups, mult, eps, hist, hist_stride, n_hist, coef);
+}
+
 // The per-token term of a layer for a few rows (decoding) in ONE launch instead of two small matrix products, the
 // gate and the post-norm: a = G h (one warp per output, rounded to T like a GEMM result), gg = gelu_tanh(a) *
 // table[tok, col0 + c], y = P gg (rounded to T), then the post-norm tail.  h: the row as the matrix products read it
@@ -221,6 +246,29 @@ __global__ void glu_clamped_kernel(T* __restrict__ out, const T* __restrict__ in
   }
 }
 
+// the clamped GLU fed by the split-K partials of the [gate | up] product (see postnorm_residual_splitk_kernel)
+template <typename T>
+__global__ void glu_clamped_splitk_kernel(T* __restrict__ out, const float* __restrict__ partials, W4Plan plan,
+                                          int64_t slot_stride, int64_t rows, int n, float limit, float slope) {
+  const int nv = n / 8;
+  const int64_t total = rows * nv;
+  for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+       idx += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t r = idx / nv;
+    const int j = (int)(idx - r * nv);
+    const float* prow = partials + r * (2 * (int64_t)n);
+    float g[8], u[8];
+    w4_sum_partials8(g, prow + j * 8, slot_stride, w4_contrib_col(plan, j * 8));
+    w4_sum_partials8(u, prow + n + j * 8, slot_stride, w4_contrib_col(plan, n + j * 8));
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const float gg = fminf(rnd<T>(g[i]), limit);
+      const float uu = fminf(fmaxf(rnd<T>(u[i]), -limit), limit);
+      out[r * n + j * 8 + i] = Num<T>::from_f(gg / (1.0f + expf(-slope * gg)) * (uu + 1.0f));
+    }
+  }
+}
+
 template <typename T>
 __global__ void token_gated_gelu_kernel(T* __restrict__ out, const T* __restrict__ in, int64_t ld_in,
                                         const T* __restrict__ table, int64_t ld_table, int col0,
@@ -296,6 +344,52 @@ int b200_postnorm_residual(float* x_out, void* h_out, const float* x_in, const v
         eps, hist, hist_stride, (int)n_hist, coef);
   });
   B200_LAUNCH_OK("postnorm_residual_kernel");
+  return B200_OK;
+}
+
+static W4Plan plan_of(const int32_t* p) {
+  W4Plan pl;
+  pl.units = p[0]; pl.P = p[1]; pl.KT = p[2]; pl.NT = p[3]; pl.slots = p[4]; pl.nsub_log2 = p[5];
+  return pl;
+}
+
+int b200_postnorm_residual_splitk(float* x_out, void* h_out, const float* x_in, const float* partials,
+                                  int64_t n_slots, const int32_t* plan6, const float* weight, int64_t rows, int64_t W,
+                                  int64_t groups, float mult, float eps, float* hist, int64_t hist_stride,
+                                  int64_t n_hist, const float* coef, int dtype, b200_stream_t stream) {
+  if (rows == 0) return B200_OK;
+  B200_CHECK_ARG(x_out && x_in && partials && plan6 && weight, "postnorm_residual_splitk: null pointer");
+  B200_CHECK_ARG(rows > 0 && W > 0 && W % 8 == 0 && groups > 0 && W % groups == 0 && (W + groups) * 4 <= 200 * 1024 &&
+                     n_slots == plan6[4] && n_slots <= W4_MAX_SLOTS && is_aligned(partials, 16),
+                 "postnorm_residual_splitk: bad shape, or the partials are not those of the given partition");
+  B200_CHECK_ARG(!hist || (n_hist > 0 && coef && hist_stride >= rows * W), "postnorm_residual_splitk: bad history");
+  auto st = static_cast<cudaStream_t>(stream);
+  const size_t smem = (size_t)(W + groups) * sizeof(float);
+  const W4Plan plan = plan_of(plan6);
+  POSTNORM_DISPATCH(dtype, {
+    if (smem > 48 * 1024)
+      B200_CUDA_OK(cudaFuncSetAttribute(postnorm_residual_splitk_kernel<T>,
+                                        cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    postnorm_residual_splitk_kernel<T><<<(unsigned)rows, kRowThreads, smem, st>>>(
+        x_out, static_cast<T*>(h_out), x_in, partials, plan, rows * W, weight, (int)W, (int)groups, mult, eps, hist,
+        hist_stride, (int)n_hist, coef);
+  });
+  B200_LAUNCH_OK("postnorm_residual_splitk_kernel");
+  return B200_OK;
+}
+
+int b200_glu_clamped_splitk(void* out, const float* partials, int64_t n_slots, const int32_t* plan6, int64_t rows,
+                            int64_t n, float limit, float slope, int dtype, b200_stream_t stream) {
+  if (rows == 0 || n == 0) return B200_OK;
+  B200_CHECK_ARG(out && partials && plan6, "glu_clamped_splitk: null pointer");
+  B200_CHECK_ARG(rows > 0 && n > 0 && n % 8 == 0 && n < (1ll << 30) && n_slots == plan6[4] &&
+                     n_slots <= W4_MAX_SLOTS && is_aligned(partials, 16),
+                 "glu_clamped_splitk: bad shape, or the partials are not those of the given partition");
+  auto st = static_cast<cudaStream_t>(stream);
+  const W4Plan plan = plan_of(plan6);
+  POSTNORM_DISPATCH(dtype, (glu_clamped_splitk_kernel<T><<<ew_grid(rows * (n / 8)), 256, 0, st>>>(
+                               static_cast<T*>(out), partials, plan, rows * 2 * n, rows, (int)n, limit, slope)));
+  B200_LAUNCH_OK("glu_clamped_splitk_kernel");
   return B200_OK;
 }
 

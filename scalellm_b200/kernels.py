@@ -896,6 +896,57 @@ def bigram_embed(table: torch.Tensor, pair_table: Optional[torch.Tensor], tokens
     return x, h
 
 
+_PLANS: Dict[Tuple[int, int], "C.Array"] = {}
+
+
+def splitk_plan(N: int, K: int):
+    """The dense split-K GEMM's partition of an [N, K] weight as the six integers its fused consumers take."""
+    key = (N, K)
+    if key not in _PLANS:
+        buf = (C.c_int32 * 6)()
+        if _lib.load().b200_dense_splitk_plan(N, K, buf) <= 0:
+            raise ValueError(f"no split-K partition for a [{N}, {K}] weight")
+        _PLANS[key] = buf
+    return _PLANS[key]
+
+
+def splitk_consumers_available() -> bool:
+    return _lib.has("b200_dense_gemm_splitk") and _lib.has("b200_dense_splitk_plan")
+
+
+def postnorm_residual_splitk(x: torch.Tensor, partials: "W4Partials", weight: torch.Tensor, groups: int, mult: float,
+                             eps: float, dtype: torch.dtype, hist: Optional[torch.Tensor] = None, n_hist: int = 0,
+                             coef: Optional[torch.Tensor] = None, x_out: Optional[torch.Tensor] = None):
+    """postnorm_residual whose y is the sum of a dense split-K GEMM's partials [slots, rows, W] rounded to `dtype`
+    (the GEMM's reduction folded into this launch)."""
+    data = partials.data
+    _cuda(x, data, weight, hist, coef)
+    _f32(x, data, weight, hist, coef)
+    S, rows, W = data.shape
+    assert x.shape == (rows, W)
+    out = x if x_out is None else x_out
+    assert hist is None or (hist.dim() == 3 and hist.shape[1:] == (rows, W) and 0 < n_hist <= hist.shape[0]
+                            and coef is not None and coef.numel() >= n_hist)
+    h = torch.empty((rows, W), dtype=dtype, device=x.device) if dtype != torch.float32 else None
+    check(_lib.load().b200_postnorm_residual_splitk(_p(out), _p(h), _p(x), _p(data), S, splitk_plan(W, partials.K),
+                                                    _p(weight), rows, W, groups, mult, eps, _p(hist),
+                                                    rows * W if hist is not None else 0, n_hist, _p(coef),
+                                                    _DT[dtype], _stream()))
+    return out, h
+
+
+def glu_clamped_splitk(partials: "W4Partials", limit: float, slope: float, dtype: torch.dtype) -> torch.Tensor:
+    """glu_clamped over the [gate | up] GEMM's split-K partials [slots, rows, 2n]."""
+    data = partials.data
+    _cuda(data)
+    _f32(data)
+    S, rows, n2 = data.shape
+    out = torch.empty((rows, n2 // 2), dtype=dtype, device=data.device)
+    check(_lib.load().b200_glu_clamped_splitk(_p(out), _p(data), S, splitk_plan(n2, partials.K), rows, n2 // 2, limit,
+                                              slope, _DT[dtype], _stream()))
+    return out
+
+
 def postnorm_residual(x: torch.Tensor, y: torch.Tensor, weight: torch.Tensor, groups: int, mult: float, eps: float,
                       hist: Optional[torch.Tensor] = None, n_hist: int = 0, coef: Optional[torch.Tensor] = None,
                       x_out: Optional[torch.Tensor] = None, want_h: bool = True):

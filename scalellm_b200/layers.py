@@ -613,6 +613,19 @@ class Linear:
             return _dense_linear(x, self.weight)
         return F.linear(x, self.weight)
 
+    def supports_partials(self, n_rows: int) -> bool:
+        """Whether the product can hand its split-K partials to a fused consumer (decode-sized bf16 steps with the
+        stream kernel in the loaded library) instead of reducing them in a launch of its own."""
+        return (_dense_partials_ok(n_rows, self.weight) and self.weight.is_contiguous()
+                and kernels.splitk_consumers_available())
+
+    def forward_partials(self, x: torch.Tensor) -> "kernels.W4Partials":
+        return kernels.dense_gemm_splitk(x, self.weight)
+
+    def forward_fusable(self, x: torch.Tensor):
+        """The product, as split-K partials where a fused consumer can take them, else as a tensor."""
+        return self.forward_partials(x) if self.supports_partials(x.shape[0]) else self.forward(x)
+
     __call__ = forward
 
 
@@ -791,11 +804,16 @@ class PostNormResidual:
         self.weight = weight.to(torch.float32).contiguous()
         self.groups, self.mult, self.eps = groups, mult, eps
 
-    def forward(self, x: torch.Tensor, y: torch.Tensor, x_out: Optional[torch.Tensor] = None,
+    def forward(self, x: torch.Tensor, y, x_out: Optional[torch.Tensor] = None,
                 hist: Optional[torch.Tensor] = None, n_hist: int = 0, coef: Optional[torch.Tensor] = None):
-        """Returns (new x fp32, the same rows in y's dtype for the next matrix product — x itself in fp32)."""
-        out, h = kernels.postnorm_residual(x, y, self.weight, self.groups, self.mult, self.eps, hist, n_hist, coef,
-                                           x_out)
+        """y: the sublayer's result, or the split-K partials of the product that makes it (Linear.forward_fusable).
+        Returns (new x fp32, the same rows in y's dtype for the next matrix product — x itself in fp32)."""
+        if isinstance(y, kernels.W4Partials):
+            out, h = kernels.postnorm_residual_splitk(x, y, self.weight, self.groups, self.mult, self.eps,
+                                                      torch.bfloat16, hist, n_hist, coef, x_out)
+        else:
+            out, h = kernels.postnorm_residual(x, y, self.weight, self.groups, self.mult, self.eps, hist, n_hist,
+                                               coef, x_out)
         return out, (h if h is not None else out)
 
     __call__ = forward
@@ -817,7 +835,7 @@ class MinGRUMixer:
         o = kernels.mingru_scan(self.in_proj(h), self.z_bias, self.x_bias, self.state, params.q_cu_seq_lens,
                                 positions, params.state_slots, params.num_sequences, self.width,
                                 params.q_max_seq_len)
-        return self.o_proj(o)
+        return self.o_proj.forward_fusable(o)
 
     __call__ = forward
 
@@ -864,7 +882,7 @@ class DiffAttention:
                               params.block_tables, params.cu_block_lens, params.token_seq, cache.block_size(),
                               self.scale, self.window, self.keep_first, self.lam, 1.0 - self.diff, self.eps,
                               params.num_sequences, params.q_max_seq_len)
-        return self.o_proj(o)
+        return self.o_proj.forward_fusable(o)
 
     __call__ = forward
 
@@ -877,8 +895,14 @@ class ClampedGLU:
         self.gate_up, self.down = Linear(torch.cat([gate, up], dim=0)), Linear(down)
         self.limit, self.slope = limit, slope
 
-    def forward(self, h: torch.Tensor) -> torch.Tensor:
-        return self.down(kernels.glu_clamped(self.gate_up(h), self.limit, self.slope))
+    def forward(self, h: torch.Tensor):
+        """The result, or the down projection's split-K partials where the post-norm can take them."""
+        gu = self.gate_up.forward_fusable(h)
+        if isinstance(gu, kernels.W4Partials):
+            act = kernels.glu_clamped_splitk(gu, self.limit, self.slope, h.dtype)
+        else:
+            act = kernels.glu_clamped(gu, self.limit, self.slope)
+        return self.down.forward_fusable(act)
 
     __call__ = forward
 

@@ -120,6 +120,10 @@ CONFIGS = {
                           (gru(30), dense(44)),
                           (attn(6, 2, 12, 20, window=7, keep_first=1, rot_dims=4, kv_from=0), None)],
                          width=48, vocab=61, groups=3, eps=1e-6, mult=1.0, scale=1.0, bigram=None, side=4),
+    # every product a multiple of 128 wide and deep: decode-sized bf16 steps hand split-K partials to fused consumers
+    "wide": config([(gru(256), dense(128, 1.5)), (attn(4, 2, 16, 32, window=11, keep_first=2, rot_dims=16, yarn=True), dense(256)),
+                    (gru(128), None), (attn(4, 2, 16, 32, window=6, keep_first=1, rot_dims=16, yarn=True, kv_from=1), dense(128))],
+                   width=128, vocab=160, groups=4, mult=0.4, side=8),
     "plain": config([(attn(2, 1, 32, 48, window=13, keep_first=2), dense(96)), (gru(100), dense(72))],
                     width=80, vocab=130, groups=1, mult=0.25, bigram=(17, 3, 1), side=0),
 }

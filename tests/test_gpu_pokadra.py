@@ -127,6 +127,35 @@ def test_clamped_glu_and_token_gate():
     assert float((o.cpu().double() - ref).abs().max()) < 1e-5
 
 
+@pytest.mark.parametrize("rows", [1, 7, 128])
+def test_consumers_of_split_k_partials(rows):
+    """Post-norm and GLU fed by the partials of the product before them against product, then kernel."""
+    from scalellm_b200 import kernels
+    if not kernels.splitk_consumers_available():
+        pytest.skip("the loaded library has no split-K stream kernel")
+    g = torch.Generator().manual_seed(rows)
+    W, K, n = 256, 384, 128
+    a = torch.randn(rows, K, generator=g).to(torch.bfloat16)
+    wo = (torch.randn(W, K, generator=g) / math.sqrt(K)).to(torch.bfloat16)
+    x, wn = torch.randn(rows, W, generator=g), torch.randn(W, generator=g)
+    hist, coef = torch.randn(3, rows, W, generator=g), torch.randn(2, generator=g)
+    y = (a.double() @ wo.double().T).to(torch.bfloat16)
+    ref, _ = kernels.postnorm_residual(x.to(DEV), y.to(DEV), wn.to(DEV), 4, 0.3, 1e-5, hist.to(DEV), 2, coef.to(DEV),
+                                       torch.empty(rows, W, device=DEV))
+    part = kernels.dense_gemm_splitk(a.to(DEV), wo.to(DEV), poison=True)
+    hd = hist.to(DEV)
+    got, h = kernels.postnorm_residual_splitk(x.to(DEV), part, wn.to(DEV), 4, 0.3, 1e-5, torch.bfloat16, hd, 2,
+                                              coef.to(DEV), torch.empty(rows, W, device=DEV))
+    assert float((got - ref).abs().max()) < 0.05 and h.dtype == torch.bfloat16      # the sums round to bf16 alike
+    assert torch.equal(hd[2].cpu(), hist[2])
+    wgu = (torch.randn(2 * n, K, generator=g) / math.sqrt(K) * 3).to(torch.bfloat16)
+    gu = (a.double() @ wgu.double().T).to(torch.bfloat16)
+    ref = kernels.glu_clamped(gu.to(DEV), 1.5, 1.702)
+    got = kernels.glu_clamped_splitk(kernels.dense_gemm_splitk(a.to(DEV), wgu.to(DEV), poison=True), 1.5, 1.702,
+                                     torch.bfloat16)
+    assert float((got.float() - ref.float()).abs().max()) < 0.06
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("W,sd,groups", [(64, 8, 1), (200, 12, 4), (48, 1, 3)])
 def test_per_token_term_in_one_launch(dtype, W, sd, groups):
