@@ -396,7 +396,7 @@ def pokadra_attention_kernels(s: dict, peaks: dict, cases=((64, 4096, 1), (4, 20
         gate = rnd(rows, H)
         f_diff = lambda: kernels.diff_attn(q, kc, vc, gate, prm.q_cu_seq_lens, prm.kv_cu_seq_lens, prm.block_tables,
                                            prm.cu_block_lens, prm.token_seq, bs, dim ** -0.5, win, keep, 0.4, 0.5, 1e-5,
-                                           batch, q_len)
+                                           batch, q_len, ctx)
         kl, vl = rnd(n_blocks * bs, Hkv, D), rnd(n_blocks * bs, Hkv, D)
         ql, ol = rnd(rows, Hl, D), torch.empty((rows, Hl, D), dtype=torch.bfloat16, device=dev)
         f_llama = lambda: kernels.paged_kv_varlen_mha(ol, ql, kl, vl, prm.q_cu_seq_lens, prm.kv_cu_seq_lens,

@@ -730,7 +730,8 @@ diff_attn_prefill_kernel(__nv_bfloat16* __restrict__ out, int64_t ldo, const flo
 // (all at the row's position), so one pass over the group's keys serves every head that shares them.  One CTA per
 // (row, group[, chunk of 16 heads]); tiles of 64 keys are staged as above and each of the 4 warps takes 16 keys of
 // every tile with accumulators of its own; the warps' running maxima, sums and weighted sums are merged through
-// shared memory at the end.
+// shared memory at the end.  A row's tiles may be shared out over n_splits such CTAs (few rows, many SMs): each then
+// hands its merged sums to diff_attn_merge_kernel through a workspace.
 // ------------------------------------------------------------------------------------------------------------
 constexpr int kDK = 64;
 constexpr int kDS = 2;     // staged tiles: one in flight while one is consumed (a third bought nothing: the walk of a
@@ -744,7 +745,7 @@ diff_attn_decode_tc_kernel(__nv_bfloat16* __restrict__ out, int64_t ldo, const f
                            const int* __restrict__ kv_cu, const int* __restrict__ block_tables,
                            const int* __restrict__ cu_block_lens, const int* __restrict__ token_seq, int H, int G,
                            int dim, int vdim, int block_size, float scale, int window, int keep_first, float lambda,
-                           float out_scale, float eps, int tile_bytes) {
+                           float out_scale, float eps, int n_splits, float* __restrict__ ws) {
   extern __shared__ __align__(16) unsigned char smraw[];
   const int KROW = 2 * dim + 8, VROW = vdim + 8;
   __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(smraw);     // [16][KROW]
@@ -753,8 +754,7 @@ diff_attn_decode_tc_kernel(__nv_bfloat16* __restrict__ out, int64_t ldo, const f
   __nv_bfloat16* Ks = reinterpret_cast<__nv_bfloat16*>(big);       // [kDS][kDK][KROW]
   __nv_bfloat16* Vs = Ks + kDS * kDK * KROW;                         // [kDS][kDK][VROW]
   float* o_s = reinterpret_cast<float*>(big);                      // after the walk: [4 warps][2 maps][16][vdim]
-  (void)tile_bytes;
-  const int row = blockIdx.x, g = blockIdx.y, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int row = blockIdx.x / n_splits, split = blockIdx.x % n_splits, g = blockIdx.y, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int R = H / G, h_base = blockIdx.z * 16;
   const int n_heads = R - h_base < 16 ? R - h_base : 16;           // valid rows of the tile
   const int seq = token_seq[row];
@@ -771,8 +771,15 @@ diff_attn_decode_tc_kernel(__nv_bfloat16* __restrict__ out, int64_t ldo, const f
   const int ns = keep_first < lo ? keep_first : lo;
   const int sink_tiles = (ns + kDK - 1) / kDK;
   const int wt0 = lo / kDK > sink_tiles ? lo / kDK : sink_tiles;
-  const int n_tiles = sink_tiles + (i / kDK - wt0 + 1);
-  auto tile_j0 = [&](int idx) { return (idx < sink_tiles ? idx : wt0 + idx - sink_tiles) * kDK; };
+  const int all_tiles = sink_tiles + (i / kDK - wt0 + 1);
+  // this CTA's share of the row's tiles (n_splits CTAs per row; an empty share hands on sums of zero)
+  const int per = (all_tiles + n_splits - 1) / n_splits;
+  const int tile0 = split * per;
+  const int n_tiles = all_tiles - tile0 < per ? (all_tiles - tile0 > 0 ? all_tiles - tile0 : 0) : per;
+  auto tile_j0 = [&](int idx) {
+    const int t = tile0 + idx;
+    return (t < sink_tiles ? t : wt0 + t - sink_tiles) * kDK;
+  };
   const size_t k_stride = (size_t)G * 2 * dim, v_stride = (size_t)G * vdim;
   auto load_tile = [&](int idx, int buf) {
     const int j0 = tile_j0(idx);
@@ -920,6 +927,27 @@ diff_attn_decode_tc_kernel(__nv_bfloat16* __restrict__ out, int64_t ldo, const f
         L[m] += f[m][w] * lw;
       }
     }
+    const int h = g * R + h_base + rr;
+    if (ws) {
+      // one of several CTAs of this row: hand on (M, L) per map and the two unnormalised sums; the merge kernel ends
+      float* dst = ws + (((size_t)row * H + h) * n_splits + split) * (size_t)(4 + 2 * vdim);
+      if (lane == 0) { dst[0] = M[0]; dst[1] = L[0]; dst[2] = M[1]; dst[3] = L[1]; }
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        const int col = lane + 32 * c;
+        if (col < vdim) {
+          float x1 = 0.0f, x2 = 0.0f;
+#pragma unroll
+          for (int w = 0; w < 4; ++w) {
+            x1 += f[0][w] * o_s[((size_t)(w * 2 + 0) * 16 + rr) * vdim + col];
+            x2 += f[1][w] * o_s[((size_t)(w * 2 + 1) * 16 + rr) * vdim + col];
+          }
+          dst[4 + col] = x1;
+          dst[4 + vdim + col] = x2;
+        }
+      }
+      continue;
+    }
     float d[4], ss = 0.0f;                               // vdim <= 128: up to 4 channels per lane
 #pragma unroll
     for (int c = 0; c < 4; ++c) {
@@ -937,7 +965,6 @@ diff_attn_decode_tc_kernel(__nv_bfloat16* __restrict__ out, int64_t ldo, const f
       }
     }
     ss = warp_sum(ss);
-    const int h = g * R + h_base + rr;
     const float gl = gate ? 1.0f / (1.0f + expf(-__bfloat162float(gate[(size_t)row * ldg + h]))) : 1.0f;
     const float fo = out_scale * gl / sqrtf(ss / (float)vdim + eps);
 #pragma unroll
@@ -945,6 +972,55 @@ diff_attn_decode_tc_kernel(__nv_bfloat16* __restrict__ out, int64_t ldo, const f
       const int col = lane + 32 * c;
       if (col < vdim) out[(size_t)row * ldo + (size_t)h * vdim + col] = __float2bfloat16_rn(d[c] * fo);
     }
+  }
+}
+
+// The end of the walk for rows whose keys were shared out over n_splits CTAs: one warp per (row, head) merges the
+// shares' maxima, sums and weighted sums, then the difference of the maps, the head's root mean square and the gate.
+__global__ void __launch_bounds__(128)
+diff_attn_merge_kernel(__nv_bfloat16* __restrict__ out, int64_t ldo, const float* __restrict__ ws,
+                       const __nv_bfloat16* __restrict__ gate, int64_t ldg, int64_t n_pairs, int H, int vdim,
+                       int n_splits, float lambda, float out_scale, float eps) {
+  const int64_t pair = (int64_t)blockIdx.x * 4 + (threadIdx.x >> 5);      // row * H + head
+  const int lane = threadIdx.x & 31;
+  if (pair >= n_pairs) return;
+  const int64_t row = pair / H;
+  const int h = (int)(pair - row * H);
+  const float* src = ws + (size_t)pair * n_splits * (size_t)(4 + 2 * vdim);
+  const size_t stride = (size_t)(4 + 2 * vdim);
+  float M[2] = {-INFINITY, -INFINITY}, L[2] = {0.0f, 0.0f};
+  for (int s = 0; s < n_splits; ++s) {
+    M[0] = fmaxf(M[0], src[s * stride + 0]);
+    M[1] = fmaxf(M[1], src[s * stride + 2]);
+  }
+  float x1[4] = {0.0f, 0.0f, 0.0f, 0.0f}, x2[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+  for (int s = 0; s < n_splits; ++s) {
+    const float* p = src + s * stride;
+    const float f1 = p[1] > 0.0f ? expf(p[0] - M[0]) : 0.0f, f2 = p[3] > 0.0f ? expf(p[2] - M[1]) : 0.0f;
+    L[0] += f1 * p[1];
+    L[1] += f2 * p[3];
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      const int col = lane + 32 * c;
+      if (col < vdim) {
+        x1[c] += f1 * p[4 + col];
+        x2[c] += f2 * p[4 + vdim + col];
+      }
+    }
+  }
+  float d[4], ss = 0.0f;
+#pragma unroll
+  for (int c = 0; c < 4; ++c) {
+    d[c] = lane + 32 * c < vdim ? x1[c] / L[0] - lambda * (x2[c] / L[1]) : 0.0f;
+    ss += d[c] * d[c];
+  }
+  ss = warp_sum(ss);
+  const float gl = gate ? 1.0f / (1.0f + expf(-__bfloat162float(gate[row * ldg + h]))) : 1.0f;
+  const float fo = out_scale * gl / sqrtf(ss / (float)vdim + eps);
+#pragma unroll
+  for (int c = 0; c < 4; ++c) {
+    const int col = lane + 32 * c;
+    if (col < vdim) out[row * ldo + (size_t)h * vdim + col] = __float2bfloat16_rn(d[c] * fo);
   }
 }
 
@@ -1135,7 +1211,8 @@ int b200_diff_attn_decode_tc(void* out, int64_t ldo, const float* q, const void*
                              const int32_t* block_tables, const int32_t* cu_block_lens, const int32_t* token_seq,
                              int64_t rows, int64_t H, int64_t G, int64_t dim, int64_t vdim, int64_t block_size,
                              float scale, int64_t window, int64_t keep_first, float lambda, float out_scale, float eps,
-                             int dtype, b200_stream_t stream) {
+                             int64_t n_splits, float* workspace, int64_t workspace_floats, int dtype,
+                             b200_stream_t stream) {
   if (rows == 0) return B200_OK;
   B200_CHECK_ARG(out && q && k_cache && v_cache && q_cu_lens && kv_cu_lens && block_tables && cu_block_lens &&
                      token_seq, "diff_attn_decode_tc: null pointer");
@@ -1151,7 +1228,11 @@ int b200_diff_attn_decode_tc(void* out, int64_t ldo, const float* q, const void*
   const size_t merge = (size_t)4 * 2 * 16 * vdim * sizeof(float);
   const size_t big = tiles > merge ? tiles : merge;
   const size_t smem = (size_t)16 * (2 * dim + 8) * 2 + 4 * 2 * 2 * 16 * sizeof(float) + big;
-  dim3 grid((unsigned)rows, (unsigned)G, (unsigned)chunks);
+  B200_CHECK_ARG(n_splits >= 1 && n_splits <= 64 && rows * n_splits < (1ll << 31) &&
+                     (n_splits == 1 || (workspace && workspace_floats >= rows * H * n_splits * (4 + 2 * vdim))),
+                 "diff_attn_decode_tc: 1..64 key splits; more than one needs rows * H * splits * (4 + 2 vdim) floats");
+  float* ws = n_splits > 1 ? workspace : nullptr;
+  dim3 grid((unsigned)(rows * n_splits), (unsigned)G, (unsigned)chunks);
 #define DAD_LAUNCH(KS, VT)                                                                                     \
   do {                                                                                                         \
     if (smem > 48 * 1024)                                                                                      \
@@ -1161,7 +1242,7 @@ int b200_diff_attn_decode_tc(void* out, int64_t ldo, const float* q, const void*
         static_cast<__nv_bfloat16*>(out), ldo, q, static_cast<const __nv_bfloat16*>(k_cache),                  \
         static_cast<const __nv_bfloat16*>(v_cache), static_cast<const __nv_bfloat16*>(gate), ldg, q_cu_lens,   \
         kv_cu_lens, block_tables, cu_block_lens, token_seq, (int)H, (int)G, (int)dim, (int)vdim,               \
-        (int)block_size, scale, (int)window, (int)keep_first, lambda, out_scale, eps, (int)tiles);             \
+        (int)block_size, scale, (int)window, (int)keep_first, lambda, out_scale, eps, (int)n_splits, ws);      \
   } while (0)
   if (dim <= 64 && vdim <= 64) DAD_LAUNCH(4, 4);
   else if (dim <= 64) DAD_LAUNCH(4, 8);
@@ -1169,6 +1250,13 @@ int b200_diff_attn_decode_tc(void* out, int64_t ldo, const float* q, const void*
   else DAD_LAUNCH(8, 8);
 #undef DAD_LAUNCH
   B200_LAUNCH_OK("diff_attn_decode_tc_kernel");
+  if (ws) {
+    const int64_t n_pairs = rows * H;
+    diff_attn_merge_kernel<<<(unsigned)((n_pairs + 3) / 4), 128, 0, st>>>(
+        static_cast<__nv_bfloat16*>(out), ldo, ws, static_cast<const __nv_bfloat16*>(gate), ldg, n_pairs, (int)H,
+        (int)vdim, (int)n_splits, lambda, out_scale, eps);
+    B200_LAUNCH_OK("diff_attn_merge_kernel");
+  }
   return B200_OK;
 }
 

@@ -1097,11 +1097,14 @@ DIFF_ATTN_DECODE_TC_MIN_GROUP = 2
 def diff_attn(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, gate: Optional[torch.Tensor],
               q_cu: torch.Tensor, kv_cu: torch.Tensor, block_tables: torch.Tensor, cu_block_lens: torch.Tensor,
               token_seq: torch.Tensor, block_size: int, scale: float, window: int, keep_first: int, lam: float,
-              out_scale: float, eps: float, n_seq: int = 0, q_max: int = 0) -> torch.Tensor:
+              out_scale: float, eps: float, n_seq: int = 0, q_max: int = 0, kv_max: int = 0,
+              n_splits: int = 0) -> torch.Tensor:
     """[rows, H * vdim] in the cache's dtype: (softmax(s1) V - lam softmax(s2) V), RMS-normalised per head, times
     out_scale and sigmoid(gate [rows, H]).  With n_seq and q_max (the step's sequence count and longest portion,
     host numbers) a step with prompt portions in bf16 runs on the tensor cores where the head sizes allow it;
-    otherwise, and for single tokens, fp32 and odd sizes, the CUDA-core kernel runs."""
+    single tokens in bf16 with grouped heads run as tensor-core tiles of heads, their keys shared out over several
+    CTAs per row when the step has few rows (kv_max: an upper bound of the cached lengths, sizes the split;
+    n_splits forces it); fp32 and odd sizes run the CUDA-core kernels."""
     _cuda(q, k_cache, v_cache, gate)
     _f32(q)
     _check_i32(q_cu, kv_cu, block_tables, cu_block_lens, token_seq)
@@ -1124,7 +1127,17 @@ def diff_attn(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, gat
             scale, window, keep_first, lam, out_scale, eps, _dt(k_cache), _stream())
     if (impl not in ("simt", "simt_decode") and H // G >= DIFF_ATTN_DECODE_TC_MIN_GROUP
             and lib.b200_diff_attn_prefill_supported(dim, vdim, _dt(k_cache))):
-        check(lib.b200_diff_attn_decode_tc(*args))      # the group's heads as the rows of a tensor-core tile
+        if n_splits <= 0:       # only steps with fewer CTAs than SMs are split (measured: a split of 256 CTAs costs more
+            # in per-CTA set-up and merging than it gains), to about two CTAs per SM, two 64-key tiles each at least
+            visible = min(kv_max, window + keep_first) if window > 0 and kv_max > 0 else kv_max
+            tiles = max(1, -(-visible // 64) + (1 if keep_first else 0))
+            ctas = rows * G * -(-(H // G) // 16)
+            n_splits = max(1, min(296 // ctas, tiles // 2, 64))
+        ws = None
+        if n_splits > 1:
+            ws = torch.empty(rows * H * n_splits * (4 + 2 * vdim), dtype=torch.float32, device=q.device)
+        check(lib.b200_diff_attn_decode_tc(*args[:-2], n_splits, _p(ws), ws.numel() if ws is not None else 0,
+                                           *args[-2:]))     # the group's heads as the rows of a tensor-core tile
         return out
     check(lib.b200_diff_attn(_p(out), H * vdim, _p(q), _p(k_cache), _p(v_cache), _p(gate),
                              gate.stride(0) if gate is not None else 0, _p(q_cu), _p(kv_cu),

@@ -881,7 +881,7 @@ class DiffAttention:
         o = kernels.diff_attn(q, cache.key_cache, cache.value_cache, gate, params.q_cu_seq_lens, params.kv_cu_seq_lens,
                               params.block_tables, params.cu_block_lens, params.token_seq, cache.block_size(),
                               self.scale, self.window, self.keep_first, self.lam, 1.0 - self.diff, self.eps,
-                              params.num_sequences, params.q_max_seq_len)
+                              params.num_sequences, params.q_max_seq_len, params.kv_max_seq_len)
         return self.o_proj.forward_fusable(o)
 
     __call__ = forward

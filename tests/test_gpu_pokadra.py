@@ -225,7 +225,7 @@ def test_mingru_in_portions_from_a_dirty_slot(dtype, width):
     assert float((state[2].cpu().double() - S).abs().max()) < 1e-5 and float(state[1].min()) == 7.0
 
 
-def _attend_case(dtype, H, G, dim, vdim, window, keep, block_size, cached, n_new, loud, seed=0):
+def _attend_case(dtype, H, G, dim, vdim, window, keep, block_size, cached, n_new, loud, seed=0, n_splits=0):
     """The attention kernel alone over a hand-made cache: the first map's query of row i points along key `loud[i]`,
     so that this key (if it is visible) takes most of the row's weight in that map.  Returns (got, want)."""
     from scalellm_b200 import kernels
@@ -254,7 +254,7 @@ def _attend_case(dtype, H, G, dim, vdim, window, keep, block_size, cached, n_new
     lam, diff, scale = 0.45, 0.3, 1.0 / math.sqrt(dim)
     got = kernels.diff_attn(q.to(DEV), kc.to(DEV), vc.to(DEV), gate.to(DEV), par.q_cu_seq_lens, par.kv_cu_seq_lens,
                             par.block_tables, par.cu_block_lens, par.token_seq, block_size, scale, window, keep, lam,
-                            1.0 - diff, 1e-5, 1, n_new)       # prompt-sized bf16 cases take the tensor-core kernel
+                            1.0 - diff, 1e-5, 1, n_new, cached + n_new, n_splits)   # prompt-sized bf16 cases take the tensor-core kernel
     mask = {"size": window, "keep_first": keep} if window else None
     want = op.diff_attend(q.double(), K.double(), V.double(), pos, scale, mask, lam, diff, 1e-5)
     want = want * torch.sigmoid(gate.double())[:, :, None]
@@ -280,8 +280,9 @@ def test_attention_window_and_kept_tokens_edges(dtype, H, G, dim, vdim):
         assert op.visible(cached + row, j, {"size": window, "keep_first": keep})
     # one decoded token with everything cached, then the same without a window: key 1 of 300 decides
     for win, kp in ((10, 3), (0, 0), (7, 0)):
-        got, want = _attend_case(dtype, H, G, dim, vdim, win, kp, 8, 300, 1, [1], seed=7)
-        assert float((got - want).abs().max()) < tol
+        for n_splits in (0, 1, 2, 3, 9):      # the row's key tiles shared out over several CTAs, some left empty
+            got, want = _attend_case(dtype, H, G, dim, vdim, win, kp, 8, 300, 1, [1], seed=7, n_splits=n_splits)
+            assert float((got - want).abs().max()) < tol, (win, kp, n_splits)
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
