@@ -63,6 +63,41 @@ __device__ __forceinline__ void postnorm_tail(float* __restrict__ x_out, T* __re
   }
   __syncthreads();
   const size_t base = (size_t)row * W;
+  // four channels per thread and step where a group of four lies inside one norm group and rows start on 16 bytes
+  const bool vec = gs % 4 == 0 && ((reinterpret_cast<uintptr_t>(x_in) | reinterpret_cast<uintptr_t>(x_out) |
+                                    reinterpret_cast<uintptr_t>(w) | reinterpret_cast<uintptr_t>(hist) |
+                                    reinterpret_cast<uintptr_t>(h_out)) & 15) == 0 && hist_stride % 4 == 0;
+  if (vec) {
+    for (int i = threadIdx.x * 4; i < W; i += (int)blockDim.x * 4) {
+      const float4 xv = *reinterpret_cast<const float4*>(x_in + base + i);
+      const float4 wv = *reinterpret_cast<const float4*>(w + i);
+      const float rg = r_s[i / gs] * mult;
+      float4 r;
+      r.x = xv.x + rg * y_s[i] * wv.x;
+      r.y = xv.y + rg * y_s[i + 1] * wv.y;
+      r.z = xv.z + rg * y_s[i + 2] * wv.z;
+      r.w = xv.w + rg * y_s[i + 3] * wv.w;
+      if (hist) {
+        *reinterpret_cast<float4*>(hist + (size_t)(n_hist - 1) * hist_stride + base + i) = r;
+        const float cl = coef[n_hist - 1];
+        float4 acc = make_float4(cl * r.x, cl * r.y, cl * r.z, cl * r.w);
+        for (int j = n_hist - 2; j >= 0; --j) {
+          const float4 hv = *reinterpret_cast<const float4*>(hist + (size_t)j * hist_stride + base + i);
+          const float cj = coef[j];
+          acc.x += cj * hv.x; acc.y += cj * hv.y; acc.z += cj * hv.z; acc.w += cj * hv.w;
+        }
+        r = acc;
+      }
+      *reinterpret_cast<float4*>(x_out + base + i) = r;
+      if (h_out) {
+        h_out[base + i] = Num<T>::from_f(r.x);
+        h_out[base + i + 1] = Num<T>::from_f(r.y);
+        h_out[base + i + 2] = Num<T>::from_f(r.z);
+        h_out[base + i + 3] = Num<T>::from_f(r.w);
+      }
+    }
+    return;
+  }
   for (int i = threadIdx.x; i < W; i += (int)blockDim.x) {
     float r = x_in[base + i] + mult * (y_s[i] * r_s[i / gs] * w[i]);
     if (hist) {
@@ -243,6 +278,31 @@ __global__ void glu_clamped_kernel(T* __restrict__ out, const T* __restrict__ in
     const float g = fminf(Num<T>::to_f(in[r * ld_in + c]), limit);
     const float u = fminf(fmaxf(Num<T>::to_f(in[r * ld_in + n + c]), -limit), limit);
     out[idx] = Num<T>::from_f(g / (1.0f + expf(-slope * g)) * (u + 1.0f));
+  }
+}
+
+// the same, 16 bytes of gate, of up and of the result per thread and step (16-bit types; n and ld multiples of 8)
+template <typename T>
+__global__ void glu_clamped_vec_kernel(T* __restrict__ out, const T* __restrict__ in, int64_t rows, int n,
+                                       int64_t ld_in, float limit, float slope) {
+  const int nv = n / 8;
+  const int64_t total = rows * nv;
+  for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+       idx += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t r = idx / nv;
+    const int j = (int)(idx - r * nv);
+    const uint4 graw = ld_v4(in + r * ld_in + j * 8), uraw = ld_v4(in + r * ld_in + n + j * 8);
+    const T* gp = reinterpret_cast<const T*>(&graw);
+    const T* up = reinterpret_cast<const T*>(&uraw);
+    uint4 oraw;
+    T* op = reinterpret_cast<T*>(&oraw);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const float g = fminf(Num<T>::to_f(gp[i]), limit);
+      const float u = fminf(fmaxf(Num<T>::to_f(up[i]), -limit), limit);
+      op[i] = Num<T>::from_f(g / (1.0f + expf(-slope * g)) * (u + 1.0f));
+    }
+    st_v4(out + r * n + j * 8, oraw);
   }
 }
 
@@ -450,6 +510,16 @@ int b200_glu_clamped(void* out, const void* in, int64_t rows, int64_t n, int64_t
   B200_CHECK_ARG(out && in, "glu_clamped: null pointer");
   B200_CHECK_ARG(rows > 0 && n > 0 && n < (1ll << 30) && ld_in >= 2 * n, "glu_clamped: bad shape");
   auto st = static_cast<cudaStream_t>(stream);
+  if (dtype != B200_FP32 && n % 8 == 0 && ld_in % 8 == 0 && is_aligned(in, 16) && is_aligned(out, 16)) {
+    if (dtype == B200_BF16)
+      glu_clamped_vec_kernel<__nv_bfloat16><<<ew_grid(rows * (n / 8)), 256, 0, st>>>(
+          static_cast<__nv_bfloat16*>(out), static_cast<const __nv_bfloat16*>(in), rows, (int)n, ld_in, limit, slope);
+    else
+      glu_clamped_vec_kernel<__half><<<ew_grid(rows * (n / 8)), 256, 0, st>>>(
+          static_cast<__half*>(out), static_cast<const __half*>(in), rows, (int)n, ld_in, limit, slope);
+    B200_LAUNCH_OK("glu_clamped_vec_kernel");
+    return B200_OK;
+  }
   POSTNORM_DISPATCH(dtype, (glu_clamped_kernel<T><<<ew_grid(rows * n), 256, 0, st>>>(
                                static_cast<T*>(out), static_cast<const T*>(in), rows, (int)n, ld_in, limit, slope)));
   B200_LAUNCH_OK("glu_clamped_kernel");

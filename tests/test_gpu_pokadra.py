@@ -120,6 +120,11 @@ def test_clamped_glu_and_token_gate():
     out = kernels.glu_clamped(gu.to(DEV), 1.25, 1.702)
     gg, uu = gu[:, :52].double().clamp(max=1.25), gu[:, 52:].double().clamp(-1.25, 1.25)
     assert float((out.cpu().double() - gg * torch.sigmoid(1.702 * gg) * (uu + 1)).abs().max()) < 1e-5
+    for n in (56, 52, 8):       # 16-bit rows of whole 16-byte pieces take the wide kernel, others the plain one
+        gb = (3.0 * torch.randn(11, 2 * n, generator=g)).to(torch.bfloat16)
+        ob = kernels.glu_clamped(gb.to(DEV), 1.25, 1.702)
+        gg, uu = gb[:, :n].double().clamp(max=1.25), gb[:, n:].double().clamp(-1.25, 1.25)
+        assert float((ob.cpu().double() - gg * torch.sigmoid(1.702 * gg) * (uu + 1)).abs().max()) < 0.02
     a, table = torch.randn(5, 6, generator=g), torch.randn(13, 30, generator=g)
     tok = [3, 12, 0, 3, 7]
     o = kernels.token_gated_gelu(a.to(DEV), table.to(DEV), 18, torch.tensor(tok, dtype=torch.int32, device=DEV))
