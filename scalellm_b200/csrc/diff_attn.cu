@@ -497,16 +497,19 @@ __device__ __forceinline__ void split_bf16(float x, float y, uint32_t& hi, uint3
   lo = Num<__nv_bfloat16>::pack(x - __bfloat162float(xh), y - __bfloat162float(yh));
 }
 
-template <int KS_MAX, int VT_MAX>      // dim <= 16 KS_MAX, vdim <= 16 VT_MAX, both multiples of 16
+// dim <= 16 KS_MAX, vdim <= 16 VT_MAX, both multiples of 16; EXACT: dim = 16 KS_MAX and vdim = 16 VT_MAX, known to
+// the compiler (row pitches and fragment offsets become immediates, the loops lose their tests)
+template <int KS_MAX, int VT_MAX, bool EXACT>
 __global__ void __launch_bounds__(128)
 diff_attn_prefill_kernel(__nv_bfloat16* __restrict__ out, int64_t ldo, const float* __restrict__ q,
                          const __nv_bfloat16* __restrict__ k_cache, const __nv_bfloat16* __restrict__ v_cache,
                          const __nv_bfloat16* __restrict__ gate, int64_t ldg, const int* __restrict__ q_cu,
                          const int* __restrict__ kv_cu, const int* __restrict__ block_tables,
-                         const int* __restrict__ cu_block_lens, int H, int G, int dim, int vdim, int block_size,
+                         const int* __restrict__ cu_block_lens, int H, int G, int dim_rt, int vdim_rt, int block_size,
                          float scale, int window, int keep_first, float lambda, float out_scale, float eps, int RW,
                          int chunks) {
   extern __shared__ __align__(16) unsigned char smraw[];
+  const int dim = EXACT ? 16 * KS_MAX : dim_rt, vdim = EXACT ? 16 * VT_MAX : vdim_rt;
   const int KROW = 2 * dim + 8, VROW = vdim + 8;        // bf16 elements per staged row (16 bytes of padding)
   __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(smraw);     // [4][16][KROW]
   __nv_bfloat16* Ks = Qs + 4 * 16 * KROW;                          // [2][kBK][KROW]
@@ -1182,21 +1185,26 @@ int b200_diff_attn_prefill(void* out, int64_t ldo, const float* q, const void* k
   B200_CHECK_ARG(G * chunks <= 65535, "diff_attn_prefill: too many heads");
   const size_t smem = ((size_t)(4 * 16 + 2 * kBK) * (2 * dim + 8) + (size_t)2 * kBK * (vdim + 8)) * 2;
   dim3 grid((unsigned)((q_max + BQ - 1) / BQ), (unsigned)n_seq, (unsigned)(G * chunks));
-#define DAP_LAUNCH(KS, VT)                                                                                     \
+#define DAP_LAUNCH(KS, VT, EX)                                                                                   \
   do {                                                                                                         \
     if (smem > 48 * 1024)                                                                                      \
-      B200_CUDA_OK(cudaFuncSetAttribute(diff_attn_prefill_kernel<KS, VT>,                                      \
+      B200_CUDA_OK(cudaFuncSetAttribute(diff_attn_prefill_kernel<KS, VT, EX>,                                  \
                                         cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));              \
-    diff_attn_prefill_kernel<KS, VT><<<grid, 128, smem, st>>>(                                                 \
+    diff_attn_prefill_kernel<KS, VT, EX><<<grid, 128, smem, st>>>(                                                 \
         static_cast<__nv_bfloat16*>(out), ldo, q, static_cast<const __nv_bfloat16*>(k_cache),                  \
         static_cast<const __nv_bfloat16*>(v_cache), static_cast<const __nv_bfloat16*>(gate), ldg, q_cu_lens,   \
         kv_cu_lens, block_tables, cu_block_lens, (int)H, (int)G, (int)dim, (int)vdim, (int)block_size, scale,  \
         (int)window, (int)keep_first, lambda, out_scale, eps, RW, chunks);                                     \
   } while (0)
-  if (dim <= 64 && vdim <= 64) DAP_LAUNCH(4, 4);
-  else if (dim <= 64) DAP_LAUNCH(4, 8);
-  else if (vdim <= 64) DAP_LAUNCH(8, 4);
-  else DAP_LAUNCH(8, 8);
+  if (dim == 64 && vdim == 128) DAP_LAUNCH(4, 8, true);          // common head shapes, sizes known to the compiler
+  else if (dim == 128 && vdim == 128) DAP_LAUNCH(8, 8, true);
+  else if (dim == 64 && vdim == 64) DAP_LAUNCH(4, 4, true);
+  else if (dim == 32 && vdim == 64) DAP_LAUNCH(2, 4, true);
+  else if (dim == 32 && vdim == 32) DAP_LAUNCH(2, 2, true);
+  else if (dim <= 64 && vdim <= 64) DAP_LAUNCH(4, 4, false);
+  else if (dim <= 64) DAP_LAUNCH(4, 8, false);
+  else if (vdim <= 64) DAP_LAUNCH(8, 4, false);
+  else DAP_LAUNCH(8, 8, false);
 #undef DAP_LAUNCH
   B200_LAUNCH_OK("diff_attn_prefill_kernel");
   return B200_OK;

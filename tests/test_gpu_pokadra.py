@@ -268,7 +268,8 @@ def _attend_case(dtype, H, G, dim, vdim, window, keep, block_size, cached, n_new
 
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("H,G,dim,vdim", [(4, 2, 16, 24), (3, 3, 20, 8), (2, 1, 64, 130), (8, 2, 48, 80), (2, 2, 64, 128),
-                                          (3, 1, 32, 16), (6, 2, 128, 64), (16, 2, 16, 32), (2, 2, 8, 12), (5, 1, 8, 16), (34, 1, 16, 16)])
+                                          (3, 1, 32, 16), (6, 2, 128, 64), (16, 2, 16, 32), (2, 2, 8, 12), (5, 1, 8, 16), (34, 1, 16, 16), (4, 2, 128, 128), (2, 1, 64, 64),
+                                          (4, 4, 32, 64), (4, 1, 32, 32)])
 def test_attention_window_and_kept_tokens_edges(dtype, H, G, dim, vdim):
     """Decoded rows (one new token each) and prompt rows whose loud key lies just inside / just outside the window,
     on the last kept token / the first one not kept, and far back with no window at all."""
